@@ -4,6 +4,7 @@ from .base import (ConfigError, LayerCall, LayerSpec, ModelConfig, architecture_
 from .qwen3 import Qwen3Config
 from .vedizen import VedizenConfig
 from .pogarax import PogaraxConfig
+from .gamanex import GamanexConfig
 
 
 def _register_builtin() -> None:
@@ -11,6 +12,7 @@ def _register_builtin() -> None:
     register_architecture("Qwen3ForCausalLM", Qwen3Config, build_decoder)
     register_architecture("Vedizen", VedizenConfig, build_decoder)
     register_architecture("Pogarax", PogaraxConfig, build_decoder)
+    register_architecture("Gamanex", GamanexConfig, build_decoder)
 
 
 _register_builtin()

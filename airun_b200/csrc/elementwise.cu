@@ -49,7 +49,8 @@ AIRUN_EXPORT int airun_embed(const void* table, int table_dtype, const int32_t* 
 template <typename TOut, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                const float* __restrict__ w, TOut* __restrict__ out,
-                               const int32_t* __restrict__ rows, int n, float eps, int write_back) {
+                               const int32_t* __restrict__ rows, int n, float eps, int write_back,
+                               const float* __restrict__ w2, TOut* __restrict__ out2) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[33];
@@ -58,6 +59,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     float* xr = x + (size_t)src * n;
     const float* dr = delta ? delta + (size_t)src * n : nullptr;
     TOut* outr = out + (size_t)r * n;
+    TOut* outr2 = out2 ? out2 + (size_t)r * n : nullptr;      // the same row under a second weight
     const int nv = n / VEC;                       // vectors in the row
     float keep[KEEP][VEC];
     float ss = 0.0f;
@@ -117,6 +119,10 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
                 outr[i * VEC + e] = from_f32<TOut>(keep[k][e] * inv * (w ? w[i * VEC + e] : 1.0f));
+            if (outr2) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) outr2[i * VEC + e] = from_f32<TOut>(keep[k][e] * inv * w2[i * VEC + e]);
+            }
         }
     }
     for (int i = threadIdx.x + KEEP * blockDim.x; i < nv; i += blockDim.x) {
@@ -125,6 +131,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
             float v = xr[i * VEC + e];
             if (dr && !write_back) v += dr[i * VEC + e];
             outr[i * VEC + e] = from_f32<TOut>(v * inv * (w ? w[i * VEC + e] : 1.0f));
+            if (outr2) outr2[i * VEC + e] = from_f32<TOut>(v * inv * w2[i * VEC + e]);
         }
     }
 }
@@ -137,7 +144,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 template <typename TOut>
 __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                                            const float* __restrict__ w, TOut* __restrict__ out,
-                                                           int n_rows, int n, float eps, int write_back) {
+                                                           int n_rows, int n, float eps, int write_back,
+                                                           const float* __restrict__ w2, TOut* __restrict__ out2) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -147,6 +155,8 @@ __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x
     const float4* dr = delta ? reinterpret_cast<const float4*>(delta + (size_t)row * n) : nullptr;
     const float4* w4 = reinterpret_cast<const float4*>(w);
     TOut* outr = out + (size_t)row * n;
+    TOut* outr2 = out2 ? out2 + (size_t)row * n : nullptr;
+    const float4* w24 = reinterpret_cast<const float4*>(w2);
     const int nv = n >> 2;
     float ss = 0.0f;
     const bool rewrite = dr && write_back;
@@ -204,25 +214,38 @@ __global__ __launch_bounds__(256) void rmsnorm_rows_kernel(float* __restrict__ x
                 pk.y = *reinterpret_cast<uint32_t*>(&hi);
                 reinterpret_cast<uint2*>(outr)[i] = pk;
             }
+            if (outr2) {
+                const float4 g2 = w24[i];
+                const float a2 = v[u].x * inv * g2.x, b2 = v[u].y * inv * g2.y, c2 = v[u].z * inv * g2.z, e2 = v[u].w * inv * g2.w;
+                if (sizeof(TOut) == 4) {
+                    reinterpret_cast<float4*>(outr2)[i] = make_float4(a2, b2, c2, e2);
+                } else {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(a2, b2), hi = __floats2bfloat162_rn(c2, e2);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                    reinterpret_cast<uint2*>(outr2)[i] = pk;
+                }
+            }
         }
     }
 }
 
-AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
-                               const int32_t* rows, int n_rows, int n, float eps, int write_back,
-                               cudaStream_t stream) {
-    if (n_rows < 0 || n <= 0) return AIRUN_ERR_ARG;
+static int rmsnorm_launch(float* x, const float* delta, const float* w, void* out, int out_dtype,
+                          const int32_t* rows, int n_rows, int n, float eps, int write_back,
+                          const float* w2, void* out2, cudaStream_t stream) {
+    if (n_rows < 0 || n <= 0 || ((w2 == nullptr) != (out2 == nullptr))) return AIRUN_ERR_ARG;
     if (rows && write_back) return AIRUN_ERR_ARG;
     if (n_rows == 0) return AIRUN_OK;
     const bool vec = n % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
-    if (vec && !rows && n_rows >= 256 && n >= 512 && (((uintptr_t)out | (uintptr_t)w) & 15) == 0) {
+    if (vec && !rows && n_rows >= 256 && n >= 512 && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)out2 | (uintptr_t)w2) & 15) == 0) {
         // enough warps per block that the blocks still cover the SMs twice
         const int wpb = n_rows >= 2368 ? 8 : n_rows >= 1184 ? 4 : 2;
         const int blocks = (n_rows + wpb - 1) / wpb;
         if (out_dtype == AIRUN_DT_F32)
-            airun_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (float*)out, n_rows, n, eps, write_back);
+            airun_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (float*)out, n_rows, n, eps, write_back, w2, (float*)out2);
         else if (out_dtype == AIRUN_DT_BF16)
-            airun_launch(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (__nv_bfloat16*)out, n_rows, n, eps, write_back);
+            airun_launch(rmsnorm_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(32 * wpb), 0, stream, x, delta, w, (__nv_bfloat16*)out, n_rows, n, eps, write_back, w2, (__nv_bfloat16*)out2);
         else
             return AIRUN_ERR_UNSUPPORTED;
         return airun_launch_status();
@@ -233,12 +256,27 @@ AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, voi
     if (threads < 32) threads = 32;
     if (n_rows <= 64 && threads > 256 && vec) threads = 256;      // few rows: more loads in flight per thread
 #define LAUNCH(TOut, VEC) \
-    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back)
+    airun_launch(rmsnorm_kernel<TOut, VEC>, dim3(n_rows), dim3(threads), 0, stream, x, delta, w, (TOut*)out, rows, n, eps, write_back, w2, (TOut*)out2)
     if (out_dtype == AIRUN_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (out_dtype == AIRUN_DT_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return AIRUN_ERR_UNSUPPORTED;
 #undef LAUNCH
     return airun_launch_status();
+}
+
+AIRUN_EXPORT int airun_rmsnorm(float* x, const float* delta, const float* w, void* out, int out_dtype,
+                               const int32_t* rows, int n_rows, int n, float eps, int write_back,
+                               cudaStream_t stream) {
+    return rmsnorm_launch(x, delta, w, out, out_dtype, rows, n_rows, n, eps, write_back, nullptr, nullptr, stream);
+}
+
+// The same row normed once and written under two weights: out = v / rms(v) * w and out2 = v / rms(v) * w2, the
+// inputs of two sub-layers that read the residual stream side by side through norms of their own.
+AIRUN_EXPORT int airun_rmsnorm_pair(float* x, const float* delta, const float* w, void* out, const float* w2, void* out2,
+                                    int out_dtype, const int32_t* rows, int n_rows, int n, float eps, int write_back,
+                                    cudaStream_t stream) {
+    if (!w2 || !out2) return AIRUN_ERR_ARG;
+    return rmsnorm_launch(x, delta, w, out, out_dtype, rows, n_rows, n, eps, write_back, w2, out2, stream);
 }
 
 // in: [T][2*I] where blocks of `group` gate columns alternate with blocks of
@@ -580,5 +618,94 @@ AIRUN_EXPORT int airun_cast_f32(const float* in, void* out, int out_dtype, long 
     if (out_dtype == AIRUN_DT_F32) airun_launch(cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float*)out, n);
     else if (out_dtype == AIRUN_DT_BF16) airun_launch(cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, in, (__nv_bfloat16*)out, n);
     else return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+// out = f(in) element by element, in: float32 [T][n] -> out's type (rows of `out` may be strided).
+//   0: relu(z)^2   1: z * sigmoid(z)   2: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))   3: relu(z)
+__device__ __forceinline__ float unit_act(float z, int mode) {
+    if (mode == 0) { const float r = fmaxf(z, 0.0f); return r * r; }
+    if (mode == 1) return z / (1.0f + expf(-z));
+    if (mode == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return fmaxf(z, 0.0f);
+}
+
+template <typename TOut>
+__global__ void act_kernel(const float* __restrict__ in, TOut* __restrict__ out, long long total, int n, long long out_stride,
+                           int mode) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / n;
+    out[t * out_stride + (i - t * n)] = from_f32<TOut>(unit_act(in[i], mode));
+}
+
+AIRUN_EXPORT int airun_act(const float* in, void* out, int out_dtype, int T, int n, long long out_stride, int mode,
+                           cudaStream_t stream) {
+    if (T < 0 || n <= 0 || mode < 0 || mode > 3 || out_stride < n) return AIRUN_ERR_ARG;
+    const long long total = (long long)T * n;
+    if (total == 0) return AIRUN_OK;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffll) return AIRUN_ERR_ARG;
+    if (out_dtype == AIRUN_DT_F32) airun_launch(act_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, in, (float*)out, total, n, out_stride, mode);
+    else if (out_dtype == AIRUN_DT_BF16) airun_launch(act_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, in, (__nv_bfloat16*)out, total, n, out_stride, mode);
+    else return AIRUN_ERR_UNSUPPORTED;
+    return airun_launch_status();
+}
+
+// What two gated, scaled sub-layers add to the residual stream:
+//   out = s1 * sigmoid(g1 + c1) * y1 [+ s2 * sigmoid(g2 + c2) * y2]
+// y: a sub-layer's result [T][n], g: its gate's product [T][gate stride] (a column slice of a wider buffer is fine), c:
+// the gate's bias [n], s: the sub-layer's scale per channel [n]; gates and scales may each be absent (null).  All float32.
+__global__ void gated_sum_kernel(const float* __restrict__ y1, const float* __restrict__ g1, long long g1_stride,
+                                 const float* __restrict__ c1, const float* __restrict__ s1, const float* __restrict__ y2,
+                                 const float* __restrict__ g2, long long g2_stride, const float* __restrict__ c2,
+                                 const float* __restrict__ s2, float* __restrict__ out, long long total, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / n;
+    const int c = (int)(i - t * n);
+    float v = y1[i];
+    if (g1) v *= 1.0f / (1.0f + expf(-(g1[t * g1_stride + c] + (c1 ? c1[c] : 0.0f))));
+    if (s1) v *= s1[c];
+    if (y2) {
+        float u = y2[i];
+        if (g2) u *= 1.0f / (1.0f + expf(-(g2[t * g2_stride + c] + (c2 ? c2[c] : 0.0f))));
+        if (s2) u *= s2[c];
+        v += u;
+    }
+    out[i] = v;
+}
+
+AIRUN_EXPORT int airun_gated_sum(const float* y1, const float* g1, long long g1_stride, const float* c1, const float* s1,
+                                 const float* y2, const float* g2, long long g2_stride, const float* c2, const float* s2,
+                                 float* out, int T, int n, cudaStream_t stream) {
+    if (T < 0 || n <= 0 || !y1 || !out || (g1 && g1_stride < n) || (g2 && g2_stride < n)) return AIRUN_ERR_ARG;
+    const long long total = (long long)T * n;
+    if (total == 0) return AIRUN_OK;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffll) return AIRUN_ERR_ARG;
+    airun_launch(gated_sum_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, y1, g1, g1_stride, c1, s1, y2, g2, g2_stride, c2, s2,
+                 out, total, n);
+    return airun_launch_status();
+}
+
+// x *= factor, in place (a head whose logits carry a fixed factor).
+__global__ void scale_kernel(float* __restrict__ x, long long n, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= factor;
+}
+
+AIRUN_EXPORT int airun_scale(float* x, long long n, float factor, cudaStream_t stream) {
+    if (n < 0) return AIRUN_ERR_ARG;
+    if (n == 0) return AIRUN_OK;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffll) return AIRUN_ERR_ARG;
+    airun_launch(scale_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, factor);
     return airun_launch_status();
 }

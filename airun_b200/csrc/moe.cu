@@ -1,6 +1,6 @@
 // A routed feed-forward: every token goes to the `top` experts with the largest scores.
 //
-//   z = Wr h (float32),  s = sigmoid(z) or softmax(z);  the `top` largest s (equal scores: the lower id first),
+//   z = Wr h (+ a bias per expert, when the router has one) (float32),  s = sigmoid(z) or softmax(z);  the `top` largest s (equal scores: the lower id first),
 //   found as the `top` largest z: the order is the same, and float32 scores that saturate at 1 are not told apart
 //   weight = s of the chosen expert, divided by the sum of the chosen ones when `renorm`
 // The rows of a step are then sorted by expert so that every expert's rows are one segment of a buffer and a
@@ -17,9 +17,9 @@
 
 #define MOE_MAX_EXPERTS 1024
 
-// One warp per token; z [T][E] are the router's logits (a product like any other, accumulated in float32).
+// One warp per token; z [T][z_stride >= E] are the router's logits (a product like any other, accumulated in float32).
 __global__ __launch_bounds__(128) void moe_route_kernel(
-    const float* __restrict__ z, int T, int E, int top, int softmax_scores, int renorm,
+    const float* __restrict__ z, long long z_stride, const float* __restrict__ bias, int T, int E, int top, int softmax_scores, int renorm,
     const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids, float* __restrict__ wts, int32_t* __restrict__ rank,
     int32_t* __restrict__ counts) {
     pdl_trigger();
@@ -33,7 +33,7 @@ __global__ __launch_bounds__(128) void moe_route_kernel(
         for (int k = lane; k < top; k += 32) ids[(size_t)t * top + k] = -1;
         return;
     }
-    for (int e = lane; e < E; e += 32) s_score[e] = z[(size_t)t * E + e];
+    for (int e = lane; e < E; e += 32) s_score[e] = z[(size_t)t * z_stride + e] + (bias ? bias[e] : 0.0f);
     __syncwarp();
     // The choice is made on the logits: sigmoid and softmax rise with them, so the order is the same, and two large
     // logits whose scores both round to 1 are still told apart.  The score of a chosen expert is worked out afterwards.
@@ -121,14 +121,14 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(
     }
 }
 
-AIRUN_EXPORT int airun_moe_route(const float* z, int T, int E, int top, int softmax_scores, int renorm,
+AIRUN_EXPORT int airun_moe_route(const float* z, long long z_stride, const float* bias, int T, int E, int top, int softmax_scores, int renorm,
                                  const int32_t* req_of_token, int32_t* ids, float* wts, int32_t* rank, int32_t* counts,
                                  int32_t* seg, cudaStream_t stream) {
-    if (T < 0 || E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || !z || !req_of_token || !ids || !wts || !rank ||
+    if (T < 0 || E <= 0 || z_stride < E || E > MOE_MAX_EXPERTS || top <= 0 || top > E || !z || !req_of_token || !ids || !wts || !rank ||
         !counts || !seg)
         return AIRUN_ERR_ARG;
     if (T == 0) return AIRUN_OK;
-    airun_launch(moe_route_kernel, dim3(ceil_div_i(T, 4)), dim3(128), (size_t)4 * E * sizeof(float), stream, z, T, E, top,
+    airun_launch(moe_route_kernel, dim3(ceil_div_i(T, 4)), dim3(128), (size_t)4 * E * sizeof(float), stream, z, z_stride, bias, T, E, top,
                  softmax_scores, renorm, req_of_token, ids, wts, rank, counts);
     airun_launch(moe_offsets_kernel, dim3(1), dim3(32), 0, stream, (const int32_t*)counts, seg, E);
     return airun_launch_status();

@@ -650,3 +650,14 @@ def latent_attention_bf16(ctx, qlat, out, cache, part) -> bool:
              pool.shape[0], int(cache.page_size), H, R, rd, float(part.scale), int(part.window), _p(part.sink),
              1 if getattr(ctx, "decode_only", False) else 0, _p(ctx.err), _stream()), "latent_attention_mma")
     return True
+
+
+def linear_act_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
+    """out = f(x @ w^T) in bfloat16 with the activation (``ops.ACT_*``) in the product's epilogue; False: the caller
+    runs the product and the activation apart."""
+    return False
+
+
+def sigmoid_attention_bf16(ctx, q, out, cache, part) -> bool:
+    """Attention without softmax on the tensor cores; False: the caller runs the plain kernel."""
+    return False

@@ -89,7 +89,7 @@ def required_libraries(dtype: torch.dtype, head_dim: int):
     """(name, defines) of every library a model of this dtype and head size uses."""
     libs = [("elementwise", None), ("gemm_simt", None), ("qkv_post", None),
             ("attention_generic", None), ("sampling", None), ("linear_attention", None), ("diff_attention", None),
-            ("recurrent_state", None), ("latent_attention", None), ("moe", None)]
+            ("recurrent_state", None), ("latent_attention", None), ("moe", None), ("sigmoid_attention", None)]
     return libs
 
 
@@ -266,6 +266,72 @@ def cast_f32(src: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_p(src), _p(out), _dt(out), src.numel(), _stream()), "cast_f32")
 
 
+def rmsnorm_pair(x: torch.Tensor, w1: torch.Tensor, out1: torch.Tensor, w2: torch.Tensor, out2: torch.Tensor, eps: float,
+                 delta: Optional[torch.Tensor] = None) -> None:
+    """out1 = rmsnorm(x [+ delta]) * w1 and out2 = the same row * w2, in one pass; with ``delta`` the sum becomes x."""
+    _cuda(x, w1, out1, w2, out2, delta)
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x must be float32 [T, n]")
+    T, n = x.shape
+    for w in (w1, w2):
+        _need(w.dtype == torch.float32 and tuple(w.shape) == (n,) and w.is_contiguous(), "norm weights must be float32 [n]")
+    for o in (out1, out2):
+        _need(tuple(o.shape) == (T, n) and o.is_contiguous() and o.dtype == out1.dtype, "norm outputs must be [T, n] of one type")
+    if delta is not None:
+        _need(delta.dtype == torch.float32 and delta.shape == x.shape and delta.is_contiguous(), "delta must match x")
+    f = _fn("elementwise", "airun_rmsnorm_pair",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(w1), _p(out1), _p(w2), _p(out2), _dt(out1), None, T, n, float(eps),
+             1 if delta is not None else 0, _stream()), "rmsnorm_pair")
+
+
+ACT_RELU2, ACT_SILU, ACT_GELU_TANH, ACT_RELU = 0, 1, 2, 3
+ACTIVATIONS = {"relu2": ACT_RELU2, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu": ACT_RELU}
+
+
+def act(src: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+    """out = f(src) element by element: relu(z)^2, z sigmoid(z), the tanh form of GELU or relu(z) (``ACT_*``); src
+    float32 [T, n], out [T, n] in its own type (a column slice of a wider buffer is fine)."""
+    _cuda(src, out)
+    _need(src.dtype == torch.float32 and src.dim() == 2 and src.is_contiguous(), "src must be contiguous float32 [T, n]")
+    T, n = src.shape
+    _need(tuple(out.shape) == (T, n) and out.stride(1) == 1, "out must be row-major [T, n]")
+    f = _fn("elementwise", "airun_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_void_p])
+    _check(f(_p(src), _p(out), _dt(out), T, n, _row_stride(out), int(mode), _stream()), "act")
+
+
+def gated_sum(out: torch.Tensor, y1: torch.Tensor, g1: Optional[torch.Tensor] = None, c1: Optional[torch.Tensor] = None,
+              s1: Optional[torch.Tensor] = None, y2: Optional[torch.Tensor] = None, g2: Optional[torch.Tensor] = None,
+              c2: Optional[torch.Tensor] = None, s2: Optional[torch.Tensor] = None) -> None:
+    """out = s1 * sigmoid(g1 + c1) * y1 [+ s2 * sigmoid(g2 + c2) * y2]: y float32 [T, n], g float32 [T, n] (column slices
+    are fine), c and s float32 [n]; a missing g means no gate, a missing s no scale.  ``out`` may be y1."""
+    _cuda(out, y1, g1, c1, s1, y2, g2, c2, s2)
+    _need(y1.dtype == torch.float32 and y1.dim() == 2 and y1.is_contiguous(), "y1 must be contiguous float32 [T, n]")
+    T, n = y1.shape
+    _need(out.dtype == torch.float32 and out.shape == y1.shape and out.is_contiguous(), "out must match y1")
+    if y2 is not None:
+        _need(y2.dtype == torch.float32 and y2.shape == y1.shape and y2.is_contiguous(), "y2 must match y1")
+    for g in (g1, g2):
+        if g is not None:
+            _rows_f32(g, "a gate")
+            _need(tuple(g.shape) == (T, n), "a gate must be [T, n]")
+    for v in (c1, s1, c2, s2):
+        if v is not None:
+            _need(v.dtype == torch.float32 and tuple(v.shape) == (n,) and v.is_contiguous(), "biases and scales must be float32 [n]")
+    f = _fn("elementwise", "airun_gated_sum",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p])
+    _check(f(_p(y1), _p(g1), _row_stride(g1) if g1 is not None else 0, _p(c1), _p(s1), _p(y2), _p(g2),
+             _row_stride(g2) if g2 is not None else 0, _p(c2), _p(s2), _p(out), T, n, _stream()), "gated_sum")
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """x *= factor, in place."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_ takes a contiguous float32 tensor")
+    f = _fn("elementwise", "airun_scale", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(_p(x), x.numel(), float(factor), _stream()), "scale")
+
+
 # ---------------------------------------------------------------- gated linear attention
 def _rows_f32(t: torch.Tensor, what: str) -> None:
     _need(t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what} must be float32 rows (a column slice is fine)")
@@ -432,6 +498,63 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, pool: torch.Tensor, block
     _check(f(_p(q), _p(out), _row_stride(out), _p(pool), _dt(q), _p(block_table), block_table.stride(0), _p(positions),
              _p(req_of_token), T, int(num_reqs), num_pages, int(page_size), nh, nkv, D, Dv, float(scale), float(cap),
              int(chunk), int(window), float(lam), float(eps), float(out_scale), _p(err), _stream()), "diff_attention")
+
+
+# ---------------------------------------------------------------- attention without softmax
+def qk_rownorm_store(proj: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], eps: float,
+                     temp_coef: float, temp_every: int, q_out: torch.Tensor, cache, ctx, q_width: int, nkv: int, kd: int,
+                     vd: int, store: bool = True) -> None:
+    """q_out = proj[:, :q_width] / rms * q_w * (1 + temp_coef * ln((pos + 1) // temp_every + 1)); the keys (next nkv*kd
+    columns, normed over all of them with k_w) and the values (nkv*vd columns after them) go into the token's page.
+    The root mean squares run over the whole projection of a token; ``temp_every`` 0: no temperature."""
+    pool, block_table = (cache.pool, cache.block_table) if store else (None, None)
+    _cuda(proj, q_w, k_w, q_out, pool, block_table)
+    _rows_f32(proj, "proj")
+    T = proj.shape[0]
+    _need(proj.shape[1] >= q_width + (nkv * (kd + vd) if store else 0), "proj is too narrow for q, k and v")
+    _need(tuple(q_out.shape) == (T, q_width) and q_out.is_contiguous(), "q_out must be contiguous [T, q_width]")
+    for w, n in ((q_w, q_width), (k_w, nkv * kd)):
+        if w is not None:
+            _need(w.dtype == torch.float32 and tuple(w.shape) == (n,) and w.is_contiguous(), "a norm weight must be float32 of its projection's width")
+    num_pages = max_blocks = 0
+    if store:
+        num_pages = _page_args(pool, nkv, kd, vd, cache.page_size)
+        _need(pool.dtype == q_out.dtype, "q and the cache pages must share a type")
+        _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1,
+              "block_table must be int32 [R, max_blocks]")
+        max_blocks = block_table.stride(0)
+    f = _fn("sigmoid_attention", "airun_qk_rownorm_store",
+            [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(proj), _row_stride(proj), _p(q_w), _p(k_w), float(eps), float(temp_coef), int(temp_every), _p(q_out), _p(pool),
+             _dt(q_out), _p(block_table), max_blocks, _p(ctx.positions), _p(ctx.req_of_token), T, int(ctx.num_reqs), num_pages,
+             int(cache.page_size), q_width, nkv, kd, vd, 1 if store else 0, _p(ctx.err), _stream()), "qk_rownorm_store")
+
+
+def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, cache, ctx, nh: int, nkv: int, D: int, Dv: int, scale: float,
+                      dist_a: Optional[torch.Tensor], dist_b: Optional[torch.Tensor], head_c: Optional[torch.Tensor],
+                      window: int = 0) -> None:
+    """out[t, h] = sum over the visible keys j of sigmoid(scale * q . k_j - a_h * ln(1 + b_h * (pos - j)) + c_h) * v_j
+    (see csrc/sigmoid_attention.cu); float32 arithmetic, any sizes up to 256."""
+    pool, block_table = cache.pool, cache.block_table
+    _cuda(q, out, pool, block_table, dist_a, dist_b, head_c)
+    T = q.shape[0]
+    _need(tuple(q.shape) == (T, nh * D) and q.is_contiguous(), "q must be contiguous [T, heads*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == q.dtype, "out must be row-major [T, heads*Dv] of q's type")
+    _need(D <= 256 and Dv <= 256, "head sizes above 256 are not taken")
+    _need(nh % nkv == 0, "query heads must be a multiple of KV heads")
+    num_pages = _page_args(pool, nkv, D, Dv, cache.page_size)
+    _need(pool.dtype == q.dtype, "q and the cache pages must share a type")
+    for v in (dist_a, dist_b, head_c):
+        if v is not None:
+            _need(v.dtype == torch.float32 and v.numel() == nh and v.is_contiguous(), "the heads' numbers must be float32 [heads]")
+    _need((dist_a is None) == (dist_b is None), "the distance term needs both of its numbers")
+    f = _fn("sigmoid_attention", "airun_sigmoid_attention",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _row_stride(out), _p(pool), _dt(q), _p(block_table), block_table.stride(0), _p(ctx.positions),
+             _p(ctx.req_of_token), T, int(ctx.num_reqs), num_pages, int(cache.page_size), nh, nkv, D, Dv, float(scale),
+             _p(dist_a), _p(dist_b), _p(head_c), int(window), _p(ctx.err), _stream()), "sigmoid_attention")
 
 
 # ---------------------------------------------------------------- matrix products
@@ -644,21 +767,24 @@ def latent_attention(qlat: torch.Tensor, out: torch.Tensor, cache, ctx, H: int, 
 
 # ---------------------------------------------------------------- routed experts
 def moe_route(logits: torch.Tensor, top: int, softmax_scores: bool, renorm: bool, req_of_token: torch.Tensor,
-              ids: torch.Tensor, wts: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor, seg: torch.Tensor) -> None:
+              ids: torch.Tensor, wts: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor, seg: torch.Tensor,
+              bias: Optional[torch.Tensor] = None) -> None:
     """ids / wts [T, top]: every token's ``top`` experts by score (sigmoid or softmax of the router's ``logits``
     [T, E], float32) and their weights; rank [T, top]: the row's place among its expert's rows; seg [E + 1]: where each
-    expert's rows begin.  ``counts`` (int32 [E]) must be zero on entry."""
-    _cuda(logits, req_of_token, ids, wts, rank, counts, seg)
-    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be contiguous float32 [T, E]")
+    expert's rows begin.  ``counts`` (int32 [E]) must be zero on entry.  ``bias`` (float32 [E]) is added to the logits first."""
+    _cuda(logits, req_of_token, ids, wts, rank, counts, seg, bias)
+    _rows_f32(logits, "logits")
     T, E = logits.shape
     _need(E <= 1024 and 1 <= top <= E, "1 to 1024 experts, top of them a token")
     for t_, dt in ((ids, torch.int32), (wts, torch.float32), (rank, torch.int32)):
         _need(t_.dtype == dt and t_.numel() >= T * top and t_.is_contiguous(), "ids / wts / rank must be [T, top]")
     _need(counts.dtype == torch.int32 and counts.numel() >= E and seg.dtype == torch.int32 and seg.numel() >= E + 1,
           "counts / seg must be int32 [E] / [E + 1]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous(), "the router's bias must be float32 [E]")
     f = _fn("moe", "airun_moe_route",
-            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_p(logits), T, E, int(top), 1 if softmax_scores else 0, 1 if renorm else 0, _p(req_of_token),
+            [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(logits), _row_stride(logits), _p(bias), T, E, int(top), 1 if softmax_scores else 0, 1 if renorm else 0, _p(req_of_token),
              _p(ids), _p(wts), _p(rank), _p(counts), _p(seg), _stream()), "moe_route")
 
 

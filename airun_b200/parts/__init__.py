@@ -2,4 +2,4 @@
 from .base import (Part, Norm, PositionEncoding, Mixer, FeedForward, PagedKVSpec, StateSpec, NormedActivations,
                    ResidualSink, CastActivations,
                    register_part, make_part, part_factory, registered_parts)
-from . import norm, rope, attention, mlp, block, embedding, linear_attention, diff_attention, delta_rule, wkv, latent_attention, moe  # noqa: F401  (registration)
+from . import norm, rope, attention, mlp, block, embedding, linear_attention, diff_attention, delta_rule, wkv, latent_attention, moe, sigmoid_attention  # noqa: F401  (registration)

@@ -230,3 +230,119 @@ class PostNormBlock(Part):
 
 
 register_part("arrangement", "post_norm", PostNormBlock)
+
+
+class GatedParallelBlock(Part):
+    """Two norms of the same residual stream, two sub-layers side by side, each result scaled per channel and gated by
+    a sigmoid of the sub-layer's own input:
+
+        h1 = norm1(x),  h2 = norm2(x)
+        x += s1 * sigmoid(G1 h1 + c1) * mixer(h1) + s2 * sigmoid(G2 h2 + c2) * ffn(h2)
+
+    ``layer_scale`` (the vectors s, tensors ``<prefix>.ls1`` / ``.ls2``) and ``gated`` (G and c, ``<prefix>.rg1`` /
+    ``.rg1.b`` and ``.rg2`` / ``.rg2.b``) can each be left out; the feed-forward may be absent, and then so are norm2,
+    s2 and the second gate.  As with the other arrangements the add is left to whoever norms x next: the block returns
+    the sum of the two terms.  Both norms run as ONE pass over x when they are root-mean-square norms with the same
+    eps.  A sub-layer that offers ``append_input_rows`` takes its gate's matrix into its own input product (the gate
+    reads the same input) and hands the columns back (``forward(..., with_extra=True)``); otherwise the gate is a
+    product of its own."""
+    norm2_belongs_to_ffn = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], dtype: torch.dtype,
+                 prefix: str, hidden_size: int, layer_scale: bool = True, gated: bool = True,
+                 names: Optional[Dict[str, str]] = None):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.dtype = norm1, mixer, norm2, ffn, dtype
+        self.prefix, self.H = prefix, int(hidden_size)
+        self.layer_scale, self.gated = bool(layer_scale), bool(gated)
+        n = dict(scale="ls{k}", gate="rg{k}", gate_bias="rg{k}.b")
+        n.update(names or {})
+        self.n = n
+        self.scales: List[Optional[torch.Tensor]] = [None, None]
+        self.gate_w: List[Optional[torch.Tensor]] = [None, None]      # None once a sub-layer has taken the matrix
+        self.gate_b: List[Optional[torch.Tensor]] = [None, None]
+        self.gate_in_sub = [False, False]
+
+    def subs(self):
+        return (self.mixer,) if self.ffn is None else (self.mixer, self.ffn)
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
+
+    def _name(self, which: str, k: int) -> str:
+        return f"{self.prefix}.{self.n[which].format(k=k + 1)}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self.parts() for s in p.weight_specs()]
+        for k in range(len(self.subs())):
+            if self.layer_scale:
+                specs.append(WeightSpec(self._name("scale", k), (self.H,), storage="float32", init="norm"))
+            if self.gated:
+                specs += [WeightSpec(self._name("gate", k), (self.H, self.H)),
+                          WeightSpec(self._name("gate_bias", k), (self.H,), storage="float32")]
+        return specs
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.load_weights(tensors)
+        for k, sub in enumerate(self.subs()):
+            if self.layer_scale:
+                self.scales[k] = tensors[self._name("scale", k)]
+            if self.gated:
+                w = tensors.pop(self._name("gate", k))
+                self.gate_b[k] = tensors[self._name("gate_bias", k)]
+                if hasattr(sub, "append_input_rows"):
+                    sub.append_input_rows(w)
+                    self.gate_in_sub[k] = True
+                else:
+                    self.gate_w[k] = w
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def device_driven(self) -> bool:
+        return all(getattr(p, "device_driven", False) for p in self.parts())
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def accepts_normed(self) -> bool:
+        return False
+
+    def _run(self, ctx, k: int, sub, h, *args):
+        """(result, gate columns or None) of sub-layer k."""
+        if self.gate_in_sub[k]:
+            return sub.forward(ctx, h, *args, with_extra=True)
+        y = sub.forward(ctx, h, *args)
+        if not self.gated:
+            return y, None
+        from .linear import linear
+        g = ctx.ws.alloc((h.shape[0], self.H), torch.float32)
+        linear(ctx, h, self.gate_w[k], g)
+        return y, g
+
+    def forward(self, ctx, x: torch.Tensor, pending, cache, next_norm: Optional[Norm] = None):
+        from ..kernels import ops
+        T, H = x.shape
+        if not isinstance(pending, torch.Tensor):
+            pending = None
+        h1 = ctx.ws.alloc((T, H), self.dtype)
+        h2 = ctx.ws.alloc((T, H), self.dtype) if self.ffn is not None else None
+        pair = h2 is not None and hasattr(self.norm1, "fusable") and hasattr(self.norm2, "fusable") \
+            and self.norm1.fusable()[1] == self.norm2.fusable()[1]
+        if pair:
+            ops.rmsnorm_pair(x, self.norm1.fusable()[0], h1, self.norm2.fusable()[0], h2, self.norm1.fusable()[1], delta=pending)
+        else:
+            self.norm1.forward(ctx, x, h1, delta=pending)
+            if h2 is not None:
+                self.norm2.forward(ctx, x, h2)
+        y1, g1 = self._run(ctx, 0, self.mixer, h1, cache)
+        y2 = g2 = None
+        if self.ffn is not None:
+            y2, g2 = self._run(ctx, 1, self.ffn, h2)
+        if not (self.gated or self.layer_scale or y2 is not None):
+            return y1
+        ops.gated_sum(y1, y1, g1, self.gate_b[0], self.scales[0], y2, g2, self.gate_b[1], self.scales[1])
+        return y1
+
+
+register_part("arrangement", "gated_parallel", GatedParallelBlock)

@@ -41,13 +41,14 @@ class TokenEmbedding(Embedding):
 class LMHead(Head):
     """logits = W h; ``tied_to``: an embedding part whose table is W.  ``soft_cap``: logits become
     cap * tanh(logits / cap) (None: no cap, as the dense Qwen3 decoder and the reference,
-    crates/airun-core/src/runtime.rs:2632-2651)."""
+    crates/airun-core/src/runtime.rs:2632-2651).  ``scale``: logits are multiplied by it (before a cap; None or 1: not)."""
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[Embedding] = None,
-                 soft_cap: Optional[float] = None, dtype=None, device=None):
+                 soft_cap: Optional[float] = None, scale: Optional[float] = None, dtype=None, device=None):
         """``prefix``: the full name of the head's tensor (unused when tied)."""
         self.name, self.V, self.H, self.tied_to = prefix, int(vocab_size), int(hidden_size), tied_to
         self.soft_cap = None if soft_cap is None else float(soft_cap)
+        self.scale = 1.0 if scale is None else float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -58,6 +59,8 @@ class LMHead(Head):
 
     def forward(self, ctx, h: torch.Tensor, out: torch.Tensor) -> None:
         linear(ctx, h, self.weight, out)
+        if self.scale != 1.0:
+            ops.scale_(out, self.scale)
         if self.soft_cap is not None:
             ops.soft_cap(out, self.soft_cap)
 

@@ -130,3 +130,54 @@ class ClampedGLU(FeedForward):
 
 
 register_part("feed_forward", "clamped_glu", ClampedGLU)
+
+
+class ActMLP(FeedForward):
+    """A feed-forward without a gate: out = Wd f(Wu h), f one of ``ops.ACTIVATIONS`` (``relu2``: the square of
+    relu; ``silu``; ``gelu_tanh``; ``relu``).  It has the split form (parts/base.py): ``forward_core`` writes f(Wu h)
+    into a buffer the arrangement gives it and ``w_out`` is Wd."""
+    device_driven = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "relu2",
+                 dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
+        self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.activation, self.mode = activation, ops.ACTIVATIONS[activation]
+        self.dtype, self.device = dtype, device
+        n = dict(up="up", down="down")
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.w_up = self.w_out = None
+        self.core_width = self.I
+
+    def weight_specs(self) -> List[WeightSpec]:
+        nm = self.names
+        return [WeightSpec(nm["up"], (self.I, self.H)), WeightSpec(nm["down"], (self.H, self.I))]
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_out = tensors.pop(self.names["up"]), tensors.pop(self.names["down"])
+
+    def adopt_w_out(self, view: torch.Tensor) -> None:
+        self.w_out = view
+
+    def forward_core(self, ctx, h: torch.Tensor, act: torch.Tensor) -> None:
+        T = h.shape[0]
+        if h.dtype == torch.bfloat16:
+            from ..kernels import fast
+            if fast.linear_act_bf16(ctx, h, self.w_up, act, self.mode):
+                return
+        u = ctx.ws.alloc((T, self.I), torch.float32)
+        linear(ctx, h, self.w_up, u)
+        ops.act(u, act, self.mode)
+
+    def forward(self, ctx, h, sink=None):
+        T = h.shape[0]
+        act = ctx.ws.alloc((T, self.I), self.dtype)
+        self.forward_core(ctx, h, act)
+        delta = ctx.ws.alloc((T, self.H), torch.float32)
+        linear(ctx, act, self.w_out, delta)
+        return delta
+
+
+register_part("feed_forward", "act_mlp", ActMLP)

@@ -1,6 +1,7 @@
 """Routed experts: a feed-forward made of many small gated units of which every token uses a few.
 
-    z = Wr h  (float32),   s = sigmoid(z)  (or softmax(z) with ``scores="softmax"``)
+    z = Wr h  (float32; + a bias per expert with ``router_bias``),   s = sigmoid(z)  (or softmax(z) with ``scores="softmax"``;
+    softmax scores divided by the sum over the chosen ones, ``renormalize``, are the softmax over the chosen logits alone)
     the ``top`` experts with the largest s are chosen (equal scores: the lower id); the kernel orders them by z,
     which orders them as s does and still tells apart two large logits whose float32 scores both round to 1
     weight_e = s_e, divided by the sum over the chosen ones when ``renormalize``
@@ -30,7 +31,7 @@ class RoutedExperts(FeedForward):
     device_driven = True
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
-                 scores: str = "sigmoid", renormalize: bool = False, weight_on: str = "input",
+                 scores: str = "sigmoid", renormalize: bool = False, weight_on: str = "input", router_bias: bool = False,
                  dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
         self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
         self.E, self.top = int(num_experts), int(top)
@@ -41,16 +42,20 @@ class RoutedExperts(FeedForward):
         self.softmax, self.renorm, self.on_input = scores == "softmax", bool(renormalize), weight_on == "input"
         self.dtype, self.device = dtype, device
         self.group = INTERLEAVE if self.I % INTERLEAVE == 0 else self.I
-        n = dict(router="router", expert="e{e}", gate="gate", up="up", down="down")
+        self.router_bias = bool(router_bias)
+        n = dict(router="router", router_bias="router.b", expert="e{e}", gate="gate", up="up", down="down")
         n.update(names or {})
         self.n = n
-        self.w_router = self.w_gu = self.w_down = self.counts = None
+        self.w_router = self.b_router = self.w_gu = self.w_down = self.counts = None
+        self.extra_rows = 0          # rows an arrangement appended to the router's product
 
     def _name(self, e: int, which: str) -> str:
         return f"{self.prefix}.{self.n['expert'].format(e=e)}.{self.n[which]}"
 
     def weight_specs(self) -> List[WeightSpec]:
         specs = [WeightSpec(f"{self.prefix}.{self.n['router']}", (self.E, self.H))]
+        if self.router_bias:
+            specs.append(WeightSpec(f"{self.prefix}.{self.n['router_bias']}", (self.E,), storage="float32"))
         for e in range(self.E):
             specs += [WeightSpec(self._name(e, "gate"), (self.I, self.H)), WeightSpec(self._name(e, "up"), (self.I, self.H)),
                       WeightSpec(self._name(e, "down"), (self.H, self.I))]
@@ -59,6 +64,8 @@ class RoutedExperts(FeedForward):
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, nb = self.group, self.I // self.group
         self.w_router = tensors.pop(f"{self.prefix}.{self.n['router']}")
+        if self.router_bias:
+            self.b_router = tensors[f"{self.prefix}.{self.n['router_bias']}"]
         gus, downs = [], []
         for e in range(self.E):
             gate, up = tensors.pop(self._name(e, "gate")), tensors.pop(self._name(e, "up"))
@@ -69,16 +76,23 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack(downs, dim=0).contiguous()      # [E, H, I]
         self.counts = torch.zeros(self.E, dtype=torch.int32, device=self.w_router.device)
 
-    def forward(self, ctx, h: torch.Tensor, sink=None):
+    def append_input_rows(self, w: torch.Tensor) -> None:
+        """``w`` [rows, hidden] joins the router's product below the router; ``forward(..., with_extra=True)`` then
+        returns its float32 columns beside the result."""
+        self.w_router = torch.cat([self.w_router, w], dim=0).contiguous()
+        self.extra_rows = int(w.shape[0])
+
+    def forward(self, ctx, h: torch.Tensor, sink=None, with_extra: bool = False):
         T, ws, top = h.shape[0], ctx.ws, self.top
         M = T * top
         ids, rank, row_of = (ws.alloc((T, top), torch.int32) for _ in range(3))
         wts = ws.alloc((T, top), torch.float32)
         seg = ws.alloc((self.E + 1,), torch.int32)
         self.counts.zero_()
-        logits = ws.alloc((T, self.E), torch.float32)
+        logits = ws.alloc((T, self.E + self.extra_rows), torch.float32)
         linear(ctx, h, self.w_router, logits)
-        ops.moe_route(logits, top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg)
+        ops.moe_route(logits[:, :self.E], top, self.softmax, self.renorm, ctx.req_of_token, ids, wts, rank, self.counts, seg,
+                      bias=self.b_router)
         xs = ws.alloc((M, self.H), self.dtype)
         ops.moe_scatter(h, top, ids, wts, rank, seg, self.on_input, xs, row_of)
         act = ws.alloc((M, self.I), self.dtype)
@@ -94,6 +108,8 @@ class RoutedExperts(FeedForward):
         grouped_linear(ctx, act, self.w_down, ys, seg)
         delta = ws.alloc((T, self.H), torch.float32)
         ops.moe_combine(ys, top, ids, wts, row_of, not self.on_input, delta)
+        if with_extra:
+            return delta, (logits[:, self.E:] if self.extra_rows else None)
         return delta
 
 
