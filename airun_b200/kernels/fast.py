@@ -68,7 +68,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 def all_libraries():
     return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
             ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64}), ("diff_attention_mma", None),
-            ("latent_attention_mma", None)]
+            ("latent_attention_mma", None), ("sigmoid_attention_mma", None)]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -658,6 +658,64 @@ def linear_act_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mo
     return False
 
 
+SIGMOID_TILE_ROWS = 64
+SIGMOID_MIN_KEYS_PER_SLICE = 256       # a slice of a single token's keys is at least this long
+
+
+def sigmoid_attention_supported(D: int, Dv: int) -> bool:
+    return "sigmoid_attention" not in DISABLED and D <= 128 and Dv <= 128
+
+
+def plan_sigmoid_slices(n_reqs: int, nkv: int, context_len: int, slots: int) -> int:
+    """Slices the keys of a single token are cut into: enough CTAs (request x KV head x slice) to fill the machine
+    once, no slice shorter than SIGMOID_MIN_KEYS_PER_SLICE keys."""
+    units = max(1, n_reqs * nkv)
+    most = max(1, context_len // SIGMOID_MIN_KEYS_PER_SLICE)
+    return max(1, min(most, slots // units, 32))
+
+
 def sigmoid_attention_bf16(ctx, q, out, cache, part) -> bool:
-    """Attention without softmax on the tensor cores; False: the caller runs the plain kernel."""
-    return False
+    """Attention without softmax on the tensor cores (csrc/sigmoid_attention_mma.cu) for every row of the batch, prompt
+    portions and single tokens alike; False: the caller runs the plain kernel (head sizes above 128)."""
+    D, Dv, nh, nkv = part.D, part.Dv, part.nh, part.nkv
+    if q.dtype != torch.bfloat16 or cache.pool.dtype != torch.bfloat16 or not sigmoid_attention_supported(D, Dv):
+        return False
+    _cuda(q, out, cache.pool, cache.block_table, ctx.cu_tokens, ctx.context_lens, ctx.err, part.dist_a, part.dist_b, part.head_c)
+    T = q.shape[0]
+    _need(tuple(q.shape) == (T, nh * D) and q.is_contiguous(), "q must be contiguous [T, heads*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == torch.bfloat16,
+          "out must be row-major bfloat16 [T, heads*Dv]")
+    pool, bt = cache.pool, cache.block_table
+    _need(pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (D + Dv), "the cache pages do not fit the head sizes")
+    _need(q.data_ptr() % 16 == 0 and pool.data_ptr() % 16 == 0, "q and the cache pages must begin on 16-byte boundaries")
+    _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs,
+          "the batch's layout arrays are shorter than its number of requests")
+    for v in (part.dist_a, part.dist_b, part.head_c):
+        _need(v is None or (v.dtype == torch.float32 and v.numel() == nh and v.is_contiguous()), "the head numbers must be float32 [heads]")
+    common = [_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
+              _p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs)]
+    consts = [pool.shape[0], int(cache.page_size), nh, nkv, D, Dv, float(part.scale), _p(part.dist_a), _p(part.dist_b),
+              _p(part.head_c), int(part.window)]
+    sig = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]
+    csig = [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int]
+    # requests that bring ONE token go to the kernel whose product rows are the query heads of a KV head (groups of up
+    # to 16), which finds them on the device; the tile kernel then skips them
+    single = "sigmoid_group" not in DISABLED and nh // nkv <= 16
+    decode_only = bool(getattr(ctx, "decode_only", False))
+    lens = None if ctx.extras.get("device_plan") else getattr(ctx, "query_lens", None)
+    if single and (decode_only or lens is None or 1 in list(lens)):
+        context = ctx.extras.get("planning_context_len", ctx.max_context_len)
+        if part.window > 0:
+            context = min(context, part.window)
+        splits = plan_sigmoid_slices(int(ctx.num_reqs), nkv, int(context), 2 * machine(q.device).sms)
+        partial = ctx.ws.alloc((splits, T, nh * Dv), torch.float32) if splits > 1 else None
+        f = _fn("sigmoid_attention_mma", "airun_sigmoid_attention_group", sig + csig + [c_int, c_void_p, c_int, c_void_p, c_void_p])
+        _check(f(*common, *consts, splits, _p(partial), T, _p(ctx.err), _stream()), "sigmoid_attention_group")
+    if single and decode_only:
+        return True
+    # every other request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the
+    # launch only needs an upper bound of their number
+    max_tiles = (T + SIGMOID_TILE_ROWS - 1) // SIGMOID_TILE_ROWS + int(ctx.num_reqs)
+    f = _fn("sigmoid_attention_mma", "airun_sigmoid_attention_mma", sig + [c_int] + csig + [c_int, c_void_p, c_void_p])
+    _check(f(*common, max_tiles, *consts, 1 if single else 0, _p(ctx.err), _stream()), "sigmoid_attention_mma")
+    return True

@@ -358,6 +358,61 @@ def test_tensor_core_attention(nh, nkv, D, Dv, page, single):
 
 
 @gpu
+@pytest.mark.parametrize("nh,nkv,D,Dv,page", [(8, 2, 64, 64, 16), (6, 3, 24, 40, 8), (2, 1, 128, 128, 32)])
+def test_single_tokens_whose_keys_are_cut_into_slices(nh, nkv, D, Dv, page):
+    """Three single tokens with 1,500, 700 and 3 keys behind them: few enough (request, KV head) pairs that the keys
+    of each are cut over several CTAs and added up by a second kernel.  Against the equations and the plain kernel."""
+    from airun_b200.kernels import fast, ops
+    seq_lens, new_lens, temp = [1500, 700, 3], [1, 1, 1], (0.4, 300)
+    assert fast.plan_sigmoid_slices(len(seq_lens), nkv, max(seq_lens), 2 * fast.B200_SMS) > 1
+    reqs, norms, cache, (spans, ctx, q) = attention_case(seq_lens, new_lens, nh, nkv, D, Dv, page, torch.bfloat16, seed=5 + D, temp=temp)
+    a, b, c = head_numbers(nh, D + 2)
+    c = c - 3.0                                                         # hundreds of keys: keep the sums near the values' size
+    part = SimpleNamespace(nh=nh, nkv=nkv, D=D, Dv=Dv, scale=0.2, dist_a=dev(a), dist_b=dev(b), head_c=dev(c), window=0)
+    out = torch.full((3, nh * Dv), 7.0, device="cuda", dtype=torch.bfloat16)
+    assert fast.sigmoid_attention_bf16(ctx, q, out, cache, part)
+    assert int(ctx.err.item()) == 0
+    want = torch.cat([plain_attention_rows(reqs[r], norms, nh, nkv, D, Dv, 0.2, a, b, c, temp, P.to_bf16_and_back)[lo:hi]
+                      for r, (lo, hi) in enumerate(spans)])
+    # every token against its own size: the short one's slices are mostly empty and must add nothing
+    for row in range(3):
+        assert torch.allclose(out[row].cpu().double(), want[row], atol=2e-2 * float(want[row].abs().max()), rtol=2e-2), row
+    plain = torch.empty_like(out)
+    ops.sigmoid_attention(q, plain, cache, ctx, nh, nkv, D, Dv, 0.2, part.dist_a, part.dist_b, part.head_c)
+    for row in range(3):
+        assert torch.allclose(out[row].float(), plain[row].float(), atol=2e-2 * float(want[row].abs().max()), rtol=2e-2), row
+
+
+@gpu
+@pytest.mark.parametrize("new", [1, 70])
+@pytest.mark.parametrize("window", [1, 50, 64, 200])
+def test_a_window_in_both_attention_kernels(window, new):
+    """The kernels take a window for designs that have one: the key ``window`` back is out, the one before it in.
+    Values are rows of ones and queries zero, so a row's result counts its visible keys' weights."""
+    from airun_b200.kernels import fast, ops
+    nh, D, Dv, n = 2, 16, 8, 333
+    def spike(proj, n_):
+        proj[:, :nh * D] = 0.0
+        proj[:, nh * D + D:] = 1.0
+    a, b, c = torch.tensor([0.0, 0.7]), torch.tensor([1.0, 0.5]), torch.tensor([0.3, 1.0])
+    for dtype in (torch.float32, torch.bfloat16):
+        reqs, norms, cache, (spans, ctx, q) = attention_case([n], [new], nh, 1, D, Dv, 8, dtype, seed=2, spike=spike, norm=False)
+        out = torch.empty(new, nh * Dv, device="cuda", dtype=dtype)
+        part = SimpleNamespace(nh=nh, nkv=1, D=D, Dv=Dv, scale=1.0, dist_a=dev(a), dist_b=dev(b), head_c=dev(c), window=window)
+        if dtype == torch.float32:
+            ops.sigmoid_attention(q, out, cache, ctx, nh, 1, D, Dv, 1.0, part.dist_a, part.dist_b, part.head_c, window)
+        else:
+            assert fast.sigmoid_attention_bf16(ctx, q, out, cache, part)
+        for row, pos in enumerate(range(n - new, n)):
+            d = torch.arange(min(window, pos + 1), dtype=F64)
+            for h in range(nh):
+                want = torch.sigmoid(float(c[h]) - float(a[h]) * torch.log(1 + float(b[h]) * d)).sum()
+                one_more = torch.sigmoid(float(c[h]) - float(a[h]) * torch.log(torch.tensor(1 + float(b[h]) * window, dtype=F64)))
+                tol = 1e-5 * float(want) if dtype == torch.float32 else max(0.3 * float(one_more), 0.004 * float(want))
+                assert abs(float(out[row, h * Dv]) - float(want)) <= tol, (dtype, row, h)
+
+
+@gpu
 @pytest.mark.parametrize("where", ["far", "first", "page border", "itself"])
 @pytest.mark.parametrize("new", [1, 12])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
