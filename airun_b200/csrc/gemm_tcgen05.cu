@@ -190,6 +190,7 @@ struct GemmParams {
     int cluster_reduce;           // the ksplit CTAs of a tile are one cluster and add their slices through
                                   // distributed shared memory instead of the scratch
     float glu_limit, glu_slope;   // EPI_SWIGLU: 0, 0 for SwiGLU; a limit > 0 for the clamped gated unit
+    int act;                      // EPI_F32 / EPI_BF16: 0 stores the product, 1 + m an activation of it (epilogue_act)
     // grouped form of the persistent kernel: the rows of A are cut into n_seg segments (seg[e] .. seg[e + 1] - 1, device
     // memory) and segment e is multiplied by rows e * b_rows .. of the B operand (one matrix per segment, stacked)
     const int32_t* seg;
@@ -204,6 +205,19 @@ struct SmemLayout {
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
 };
+
+// An activation of 16 results in place, for feed-forwards without a gate (out = f(x W^T)):
+//   m = 0: relu(z)^2   1: z * sigmoid(z)   2: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))   3: relu(z)
+__device__ __forceinline__ void epilogue_act(float* v, int m) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float z = v[i];
+        if (m == 0) { const float r = fmaxf(z, 0.0f); v[i] = r * r; }
+        else if (m == 1) v[i] = z / (1.0f + __expf(-z));
+        else if (m == 2) v[i] = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        else v[i] = fmaxf(z, 0.0f);
+    }
+}
 
 // Epilogue for 16 consecutive accumulator columns [c0, c0+16) of this thread's row.
 template <int EPI, bool SWAP>
@@ -491,6 +505,7 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_kernel(
                 if (SWAP) store_resid_swapped(p, v, a_row, b0, c, s_ssq[quad]);
                 else ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
             } else {
+                if (p.act) epilogue_act(v, p.act - 1);
                 store_chunk<EPI, SWAP>(p, v, a_row, b0, c);
             }
         }
@@ -782,7 +797,10 @@ __global__ __launch_bounds__(GEMM_THREADS, 1) void gemm_tcgen05_persistent_kerne
                 if (!row_on) continue;
                 if (EPI == EPI_SWIGLU) store_swiglu_normal(p, v, u, a_row, b0, c);
                 else if (EPI == EPI_RESID) ssq_acc += store_resid_normal(p, v, a_row, b0 + c);
-                else store_chunk<EPI, false>(p, v, a_row, b0, c);
+                else {
+                    if (p.act) epilogue_act(v, p.act - 1);
+                    store_chunk<EPI, false>(p, v, a_row, b0, c);
+                }
             }
             if (EPI == EPI_RESID && a_row < p.a_rows) p.ssq_out[(size_t)(tile / m_tiles) * p.ssq_out_ld + a_row] = ssq_acc;
         }
@@ -1004,7 +1022,7 @@ static int gemm_launch(const void* x, const void* W, void* out, int M, int N, in
                        int ksplit, float* scratch, int* counters, int* err, cudaStream_t stream,
                        const float* ssq_in, int ssq_parts, int ssq_ld, float eps_in, int norm_size,
                        float* resid, long long ld_resid, const float* norm_w, float* ssq_out,
-                       int ssq_out_ld, float glu_limit, float glu_slope) {
+                       int ssq_out_ld, float glu_limit, float glu_slope, int act = 0) {
     if (M <= 0 || N <= 0 || K <= 0 || !err) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
     if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
@@ -1047,6 +1065,7 @@ static int gemm_launch(const void* x, const void* W, void* out, int M, int N, in
     p.err = err;
     p.glu_limit = glu_limit;
     p.glu_slope = glu_slope;
+    p.act = (epi == EPI_F32 || epi == EPI_BF16) ? act : 0;
     p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.ssq_ld = ssq_ld; p.eps_in = eps_in;
     p.inv_n_in = norm_size > 0 ? 1.0f / (float)norm_size : 0.0f;
     p.resid = resid; p.ld_resid = ld_resid; p.norm_w = norm_w; p.ssq_out = ssq_out; p.ssq_out_ld = ssq_out_ld;
@@ -1121,6 +1140,15 @@ AIRUN_EXPORT int airun_gemm_tcgen05_glu(const void* x, const void* W, void* out,
     if (!(limit > 0.0f)) return AIRUN_ERR_ARG;
     return gemm_launch(x, W, out, M, N, K, ldx, ldw, ldc, EPI_SWIGLU, swap, bn, ksplit, scratch, counters, err, stream,
                        nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0, limit, slope);
+}
+
+// out = f(x W^T) with the activation f (mode 0..3, see epilogue_act) applied to the finished sums before they are stored.
+AIRUN_EXPORT int airun_gemm_tcgen05_act(const void* x, const void* W, void* out, int M, int N, int K,
+                                        long long ldx, long long ldw, long long ldc, int epi, int swap, int bn, int ksplit,
+                                        float* scratch, int* counters, int* err, cudaStream_t stream, int mode) {
+    if ((epi != EPI_F32 && epi != EPI_BF16) || mode < 0 || mode > 3) return AIRUN_ERR_ARG;
+    return gemm_launch(x, W, out, M, N, K, ldx, ldw, ldc, epi, swap, bn, ksplit, scratch, counters, err, stream,
+                       nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0, 0.0f, 0.0f, 1 + mode);
 }
 
 AIRUN_EXPORT int airun_gemm_tcgen05(const void* x, const void* W, void* out, int M, int N, int K,

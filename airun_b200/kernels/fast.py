@@ -91,8 +91,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
                  ksplit: int, err: torch.Tensor, scratch: Optional[torch.Tensor] = None,
                  counters: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
                  eps_in: float = 0.0, norm_size: int = 0, resid: Optional[torch.Tensor] = None,
-                 norm_w: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None) -> None:
-    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes).
+                 norm_w: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None,
+                 act: Optional[int] = None) -> None:
+    """out = x @ w^T on tcgen05 (see csrc/gemm_tcgen05.cu for the modes).  ``act`` (an ``ops.ACT_*``, with EPI_F32 or
+    EPI_BF16 and nothing else folded in): out = f(x @ w^T).
 
     ``ssq_in`` [parts, M] float32: x is bfloat16(residual * norm weight) and each token's results are
     scaled by rsqrt(sum of its parts / norm_size + eps_in).  ``epi == EPI_RESID``: ``resid`` [M, N]
@@ -133,6 +135,15 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, 
     if ssq_in is not None:
         _need(ssq_in.dtype == torch.float32 and ssq_in.dim() == 2 and ssq_in.is_contiguous() and ssq_in.shape[1] >= M
               and norm_size > 0, "ssq_in must be float32 [parts, M]")
+    if act is not None:
+        _need(epi in (EPI_F32, EPI_BF16) and ssq_in is None, "an activation goes with the plain epilogues only")
+        f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_act",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                 c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int])
+        _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
+                 w.stride(0), out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)),
+                 epi, 1 if swap else 0, bn, ksplit, _p(scratch), _p(counters), _p(err), _stream(), int(act)), "gemm_tcgen05_act")
+        return
     # the build with the folded norm only where it is asked for; the plain one is leaner
     fold = {"AIRUN_FOLD_NORM": 1} if (ssq_in is not None or epi == EPI_RESID) else None
     f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_ex",
@@ -655,7 +666,11 @@ def latent_attention_bf16(ctx, qlat, out, cache, part) -> bool:
 def linear_act_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
     """out = f(x @ w^T) in bfloat16 with the activation (``ops.ACT_*``) in the product's epilogue; False: the caller
     runs the product and the activation apart."""
-    return False
+    if "linear_act" in DISABLED or not _usable(x, w) or out.dtype != torch.bfloat16 or tuple(out.shape) != (x.shape[0], w.shape[0]):
+        return False
+    swap, bn, ksplit = plan_gemm(x.shape[0], w.shape[0], x.shape[1])
+    gemm_tcgen05(x, w, out, EPI_BF16, swap, bn, ksplit, ctx.err, act=mode)
+    return True
 
 
 SIGMOID_TILE_ROWS = 64

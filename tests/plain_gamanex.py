@@ -109,8 +109,9 @@ def plain_queries(h, W, p: str, m: dict, eps: float, positions, rnd: Rounding = 
     return _r(rnd, q)
 
 
-def plain_sigmoid_attention(q, k, v, m: dict, a, b, c, first: int = 0):
-    """q [T, H*D] at positions first.., k [first + T, G*D], v [first + T, G*Dv] -> [T, H*Dv]."""
+def plain_sigmoid_attention(q, k, v, m: dict, a, b, c, first: int = 0, rnd: Rounding = None):
+    """q [T, H*D] at positions first.., k [first + T, G*D], v [first + T, G*Dv] -> [T, H*Dv].  ``rnd`` rounds the
+    weights where the tensor-core kernels hand them to the second product (they are formed in float32)."""
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T, S = q.shape[0], k.shape[0]
     see = plain_causal(T, first)
@@ -119,14 +120,14 @@ def plain_sigmoid_attention(q, k, v, m: dict, a, b, c, first: int = 0):
         g = hh // (H // G)
         s = (q[:, hh * D:(hh + 1) * D] @ k[:, g * D:(g + 1) * D].T) * m["scale"]
         s = s - plain_distance_bias(T, float(a[hh]), float(b[hh]), first).to(q.dtype)
-        w = torch.sigmoid(s + c[hh]) * see
+        w = _r(rnd, torch.sigmoid(s + c[hh]) * see)
         out[:, hh * Dv:(hh + 1) * Dv] = w @ v[:, g * Dv:(g + 1) * Dv]
     return out
 
 
 def plain_attention_mixer(h, W, p: str, m: dict, eps: float, k, v, positions, rnd: Rounding = None):
     q = plain_queries(h, W, p, m, eps, positions, rnd)
-    o = plain_sigmoid_attention(q, k, v, m, W[p + ".r1"], W[p + ".r2"], W[p + ".pb"])
+    o = plain_sigmoid_attention(q, k, v, m, W[p + ".r1"], W[p + ".r2"], W[p + ".pb"], rnd=rnd)
     return _r(rnd, o) @ W[p + ".o"].T
 
 

@@ -252,6 +252,26 @@ def test_activations_gates_and_the_scaled_head():
     assert torch.allclose(x.cpu(), 1.7 * z)
 
 
+@gpu
+@pytest.mark.parametrize("M,N,K", [(1, 320, 256), (9, 4096, 2048), (40, 512, 1024), (100, 768, 512), (300, 1024, 256), (1500, 4096, 512)])
+def test_activation_in_the_products_epilogue(M, N, K):
+    """f(x W^T) with f applied to the finished sums inside the tensor-core product, for every way the product is cut
+    (weights or tokens as the wide operand, K in slices, the persistent kernel), against float64."""
+    from airun_b200.kernels import fast, ops
+    g = torch.Generator().manual_seed(M + N)
+    x = P.to_bf16_and_back(torch.randn(M, K, generator=g))
+    w = P.to_bf16_and_back(torch.randn(N, K, generator=g) / math.sqrt(K))
+    z = x.double() @ w.double().T
+    want = {"relu2": torch.relu(z) ** 2, "silu": z * torch.sigmoid(z), "relu": torch.relu(z),
+            "gelu_tanh": 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))}
+    ctx = SimpleNamespace(err=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    for name, ref in want.items():
+        out = torch.full((M, N), 9.0, device="cuda", dtype=torch.bfloat16)
+        assert fast.linear_act_bf16(ctx, dev(x).to(torch.bfloat16), dev(w).to(torch.bfloat16), out, ops.ACTIVATIONS[name])
+        assert int(ctx.err.item()) == 0
+        assert torch.allclose(out.cpu().double(), ref, atol=1e-2, rtol=1e-2), name
+
+
 def attention_case(seq_lens, new_lens, nh, nkv, D, Dv, page, dtype, seed, temp=(0.0, 0), spike=None, norm=True):
     """Keys and values written through the prologue kernel (pages handed out in a scrambled order) for the first
     len - new tokens of every request, then the last ``new`` tokens of each as one batch.  Returns the projections,
