@@ -167,6 +167,11 @@ class GamanexConfig(ModelConfig):
     def execution_order(self) -> List[LayerCall]:
         return [LayerCall(i, cache_from=l["mixer"].get("kv_from")) for i, l in enumerate(self.layers)]
 
+    def ignorable_tensors(self) -> List[str]:
+        """Tensors a model file may hold although nothing reads them: the second norm, scale and gate of a layer that
+        has no feed-forward."""
+        return [f"l{i}.{n}" for i, l in enumerate(self.layers) if not l["mlp"] for n in ("norm2", "ls2", "rg2", "rg2.b")]
+
     def summary(self) -> str:
         moe = sum(1 for l in self.layers if l["mlp"] and l["mlp"]["kind"] == "moe")
         shared = sum(1 for l in self.layers if "kv_from" in l["mixer"])

@@ -19,8 +19,17 @@
 #define SA_WARPS 4
 #define SA_MAX_PER_LANE 8     // D <= 256 and Dv <= 256
 
+__device__ __forceinline__ void sa_store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void sa_store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+#define SA_ROW_VECS 8         // float4 a thread keeps of a projection: rows of up to 8,192 numbers are read once
+
 // One block per token: the two norms over whole projections, the temperature, q out, keys and values into the
-// token's page.  proj is float32 [T][q_width (+ nkv*kd + nkv*vd when store)].
+// token's page.  proj is float32 [T][q_width (+ nkv*kd + nkv*vd when store)].  When every width is a multiple of 4
+// (and the rows are aligned) a thread reads its part of the token's q and k once, sixteen bytes at a time, keeps it in
+// registers across the two sums and writes four results at a time; otherwise it goes number by number.
 template <typename T>
 __global__ __launch_bounds__(256) void qk_rownorm_store_kernel(
     const float* __restrict__ proj, long long proj_stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
@@ -39,6 +48,66 @@ __global__ __launch_bounds__(256) void qk_rownorm_store_kernel(
         return;
     }
     const float* row = proj + (size_t)t * proj_stride;
+    const int kw_all = nkv * kd;
+    if (((q_width | kd | vd) & 3) == 0 && (proj_stride & 3) == 0 && ((uintptr_t)proj & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+        (!store || ((uintptr_t)pool & 15) == 0) && q_width <= SA_ROW_VECS * 4 * 256 && kw_all <= SA_ROW_VECS * 4 * 256 &&
+        (!q_w || ((uintptr_t)q_w & 15) == 0) && (!k_w || ((uintptr_t)k_w & 15) == 0)) {
+        const int tid = threadIdx.x, qn = q_width >> 2, kn = kw_all >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        int page = -1;
+        if (store) {
+            const int blk = pos / page_size;
+            page = blk < max_blocks ? block_table[(size_t)req * max_blocks + blk] : -1;
+        }
+        const bool keys = store && page >= 0 && page < num_pages;
+        float4 qv[SA_ROW_VECS], kv[SA_ROW_VECS];
+        float ss = 0.0f, ks = 0.0f;
+#pragma unroll
+        for (int i = 0; i < SA_ROW_VECS; ++i) {
+            const int c = tid + i * 256;
+            qv[i] = c < qn ? row4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            kv[i] = (keys && c < kn) ? row4[qn + c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < SA_ROW_VECS; ++i) {
+            ss = fmaf(qv[i].x, qv[i].x, ss); ss = fmaf(qv[i].y, qv[i].y, ss); ss = fmaf(qv[i].z, qv[i].z, ss); ss = fmaf(qv[i].w, qv[i].w, ss);
+            ks = fmaf(kv[i].x, kv[i].x, ks); ks = fmaf(kv[i].y, kv[i].y, ks); ks = fmaf(kv[i].z, kv[i].z, ks); ks = fmaf(kv[i].w, kv[i].w, ks);
+        }
+        ss = block_sum(ss, red);
+        ks = block_sum(ks, red);
+        float inv = q_w ? rsqrtf(ss / (float)q_width + eps) : 1.0f;
+        if (temp_every > 0) inv *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+#pragma unroll
+        for (int i = 0; i < SA_ROW_VECS; ++i) {
+            const int c = tid + i * 256;
+            if (c >= qn) break;
+            const float4 w = q_w ? reinterpret_cast<const float4*>(q_w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+            sa_store4(q_out + (size_t)t * q_width + 4 * c, make_float4(qv[i].x * w.x * inv, qv[i].y * w.y * inv, qv[i].z * w.z * inv, qv[i].w * w.w * inv));
+        }
+        if (!store) return;
+        if (!keys) {
+            if (tid == 0) atomicOr(err, AIRUN_DEV_BAD_PAGE);
+            return;
+        }
+        const int slot = pos - (pos / page_size) * page_size;
+        const float kinv = k_w ? rsqrtf(ks / (float)kw_all + eps) : 1.0f;
+        T* pk = pool + (size_t)page * nkv * page_size * (kd + vd);
+        T* pv = pk + (size_t)nkv * page_size * kd;
+#pragma unroll
+        for (int i = 0; i < SA_ROW_VECS; ++i) {
+            const int c = tid + i * 256;
+            if (c >= kn) break;
+            const int g = (4 * c) / kd, e = 4 * c - g * kd;
+            const float4 w = k_w ? reinterpret_cast<const float4*>(k_w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+            sa_store4(pk + ((size_t)g * page_size + slot) * kd + e, make_float4(kv[i].x * w.x * kinv, kv[i].y * w.y * kinv, kv[i].z * w.z * kinv, kv[i].w * w.w * kinv));
+        }
+        const float4* v4 = row4 + qn + kn;
+        for (int c = tid; c < (nkv * vd) >> 2; c += 256) {
+            const int g = (4 * c) / vd, e = 4 * c - g * vd;
+            sa_store4(pv + ((size_t)g * page_size + slot) * vd + e, v4[c]);
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int c = threadIdx.x; c < q_width; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
     ss = block_sum(ss, red);

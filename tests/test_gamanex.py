@@ -155,6 +155,25 @@ def test_declared_tensors_are_the_files_tensors():
         assert specs == {n: tuple(s) for n, s in P.tensor_shapes(cfg).items()}
 
 
+def test_a_file_may_keep_the_second_norm_of_a_layer_without_feed_forward():
+    """A layer without a feed-forward reads no second norm, scale or gate; a file that holds them all the same loads,
+    any other stray tensor does not."""
+    from airun_b200.config import GamanexConfig
+    from airun_b200.engine.model import DecoderModel
+    from airun_b200.weights import DictSource, WeightError, check_source
+    cfg = shape_g1()
+    bare = next(i for i, l in enumerate(cfg["layers"]) if l["mlp"] is None)
+    W = dict(P.random_weights(cfg, seed=3))
+    width = cfg["width"]
+    W.update({f"l{bare}.norm2": torch.ones(width), f"l{bare}.ls2": torch.ones(width), f"l{bare}.rg2": torch.zeros(width, width),
+              f"l{bare}.rg2.b": torch.zeros(width)})
+    model = DecoderModel(GamanexConfig.from_dict(cfg), torch.float32, "cpu")
+    check_source(model.weight_specs(), DictSource(W), model.ignorable_tensors())
+    W[f"l{bare}.mlp.up"] = torch.zeros(4, width)
+    with pytest.raises(WeightError):
+        check_source(model.weight_specs(), DictSource(W), model.ignorable_tensors())
+
+
 def test_readers_share_their_owners_pages():
     from airun_b200.cache.manager import CacheManager
     from airun_b200.config import GamanexConfig
