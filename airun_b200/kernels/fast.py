@@ -681,12 +681,28 @@ def sigmoid_attention_supported(D: int, Dv: int) -> bool:
     return "sigmoid_attention" not in DISABLED and D <= 128 and Dv <= 128
 
 
+def sigmoid_group_resident(D: int, Dv: int) -> int:
+    """CTAs of the kernel for single tokens an SM holds at once: by their shared memory (a Q tile of 16 rows and two
+    stages of 64 keys and 64 values, padded head sizes) and their registers (up to 128 a thread)."""
+    dp, dvp = (32 if D <= 32 else 64 if D <= 64 else 128), (32 if Dv <= 32 else 64 if Dv <= 64 else 128)
+    smem = ((16 + 2 * 64) * (dp + 8) + 2 * 64 * (dvp + 8)) * 2 + 1024
+    return max(1, min(227 * 1024 // smem, 4))
+
+
 def plan_sigmoid_slices(n_reqs: int, nkv: int, context_len: int, slots: int) -> int:
-    """Slices the keys of a single token are cut into: enough CTAs (request x KV head x slice) to fill the machine
-    once, no slice shorter than SIGMOID_MIN_KEYS_PER_SLICE keys."""
+    """Slices the keys of a single token are cut into.  ``slots`` CTAs run at once and the CTAs (request x KV head x
+    slice) come in waves of that many; a CTA's time goes with the length of its slice plus what it costs to set up
+    and hand on its sums (about 32 keys' worth).  So s slices cost ceil(units * s / slots) * (context / s + 32): with
+    512 units and 444 slots one slice a token is two waves (the second nearly empty) and four slices are five waves
+    of a quarter the length.  No slice is shorter than SIGMOID_MIN_KEYS_PER_SLICE keys."""
     units = max(1, n_reqs * nkv)
-    most = max(1, context_len // SIGMOID_MIN_KEYS_PER_SLICE)
-    return max(1, min(most, slots // units, 32))
+    most = max(1, min(context_len // SIGMOID_MIN_KEYS_PER_SLICE, 32))
+    best, best_cost = 1, None
+    for s in range(1, most + 1):
+        cost = -(-units * s // max(1, slots)) * (context_len / s + 32.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def sigmoid_attention_bf16(ctx, q, out, cache, part) -> bool:
@@ -722,7 +738,7 @@ def sigmoid_attention_bf16(ctx, q, out, cache, part) -> bool:
         context = ctx.extras.get("planning_context_len", ctx.max_context_len)
         if part.window > 0:
             context = min(context, part.window)
-        splits = plan_sigmoid_slices(int(ctx.num_reqs), nkv, int(context), 2 * machine(q.device).sms)
+        splits = plan_sigmoid_slices(int(ctx.num_reqs), nkv, int(context), sigmoid_group_resident(D, Dv) * machine(q.device).sms)
         partial = ctx.ws.alloc((splits, T, nh * Dv), torch.float32) if splits > 1 else None
         f = _fn("sigmoid_attention_mma", "airun_sigmoid_attention_group", sig + csig + [c_int, c_void_p, c_int, c_void_p, c_void_p])
         _check(f(*common, *consts, splits, _p(partial), T, _p(ctx.err), _stream()), "sigmoid_attention_group")
