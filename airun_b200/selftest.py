@@ -442,6 +442,98 @@ def check_diff_attention(dev) -> Tuple[float, float]:
     return max(worst[0], worst[1] / 200), 1e-4                     # bfloat16 storage is held to 2e-2
 
 
+def check_sigmoid_attention(dev) -> Tuple[float, float]:
+    """Attention without softmax over scrambled pages (norms over the whole q and k projections, a temperature that
+    steps inside the portion, a distance term and an offset per head): the float32 kernel, then the tensor-core
+    kernels in bfloat16 (a whole prompt, a single token whose keys are cut into slices, a portion)."""
+    from types import SimpleNamespace
+    from .kernels import fast, ops
+    heads, kvh, D, Dv, page = 4, 2, 24, 40, 8
+    scale, eps, coef, every = 0.3, 1e-5, 0.5, 11
+    lens, new = [90, 700, 41], [90, 1, 7]
+    qw, kw = heads * D, kvh * D
+    worst = []
+    for dtype in (torch.float32, torch.bfloat16):
+        g = torch.Generator().manual_seed(6)
+        projs = [torch.randn(n, qw + kw + kvh * Dv, generator=g) for n in lens]
+        wq, wk = 1 + 0.2 * torch.randn(qw, generator=g), 1 + 0.2 * torch.randn(kw, generator=g)
+        a, b, c = 0.2 + torch.rand(heads, generator=g), 0.1 + torch.rand(heads, generator=g), -3.0 + torch.randn(heads, generator=g)
+        nb = [(n + page - 1) // page for n in lens]
+        perm = torch.randperm(sum(nb) + 2, generator=g).tolist()
+        bt = torch.full((3, max(nb)), -1, dtype=torch.int32)
+        for r, n in enumerate(nb):
+            for blk in range(n):
+                bt[r, blk] = perm.pop()
+        cache = SimpleNamespace(pool=torch.zeros(sum(nb) + 2, page * kvh * (D + Dv), device=dev, dtype=dtype),
+                                block_table=bt.to(dev), page_size=page, shared=False)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        for phase in (0, 1):
+            spans = [(0, n - m) if phase == 0 else (n - m, n) for n, m in zip(lens, new)]
+            counts = [hi - lo for lo, hi in spans]
+            if not sum(counts):
+                continue
+            proj = torch.cat([projs[r][lo:hi] for r, (lo, hi) in enumerate(spans)]).to(dev)
+            cu = [0]
+            for n in counts:
+                cu.append(cu[-1] + n)
+            ctx = SimpleNamespace(
+                positions=torch.cat([torch.arange(lo, hi) for lo, hi in spans]).to(dev, torch.int32),
+                req_of_token=torch.cat([torch.full((n,), r) for r, n in enumerate(counts)]).to(dev, torch.int32),
+                cu_tokens=torch.tensor(cu, dtype=torch.int32, device=dev),
+                context_lens=torch.tensor([hi for _, hi in spans], dtype=torch.int32, device=dev), num_reqs=3, err=err,
+                query_lens=counts, max_context_len=max(lens), extras={}, decode_only=False,
+                ws=SimpleNamespace(alloc=lambda shape, dt: torch.empty(shape, device=dev, dtype=dt)))
+            q = torch.empty(proj.shape[0], qw, device=dev, dtype=dtype)
+            ops.qk_rownorm_store(proj, wq.to(dev), wk.to(dev), eps, coef, every, q, cache, ctx, qw, kvh, D, Dv, store=True)
+        out = torch.empty(q.shape[0], heads * Dv, device=dev, dtype=dtype)
+        part = SimpleNamespace(D=D, Dv=Dv, nh=heads, nkv=kvh, scale=scale, dist_a=a.to(dev), dist_b=b.to(dev), head_c=c.to(dev), window=0)
+        if dtype == torch.float32:
+            ops.sigmoid_attention(q, out, cache, ctx, heads, kvh, D, Dv, scale, part.dist_a, part.dist_b, part.head_c, 0)
+        elif not fast.sigmoid_attention_bf16(ctx, q, out, cache, part):
+            raise RuntimeError("the tensor-core attention refused sizes it should take")
+        if int(err.item()):
+            raise RuntimeError("the attention reported a device error")
+        at, w = 0, 0.0
+        for r, n in enumerate(lens):
+            p64 = projs[r].double()
+            qq, kk, vv = p64[:, :qw], p64[:, qw:qw + kw], p64[:, qw + kw:].view(n, kvh, Dv)
+            i = torch.arange(n)
+            qq = qq / torch.sqrt((qq * qq).mean(-1, keepdim=True) + eps) * wq.double()
+            qq = (qq * (1 + coef * torch.log(torch.floor((i + 1) / every) + 1)).unsqueeze(1)).view(n, heads, D)
+            kk = (kk / torch.sqrt((kk * kk).mean(-1, keepdim=True) + eps) * wk.double()).view(n, kvh, D)
+            dist = (i[:, None] - i[None, :]).clamp(min=0).double()
+            ref = torch.zeros(n, heads, Dv, dtype=torch.float64)
+            for h in range(heads):
+                sc = (qq[:, h] @ kk[:, h // (heads // kvh)].T) * scale - float(a[h]) * torch.log1p(float(b[h]) * dist) + float(c[h])
+                ref[:, h] = (torch.sigmoid(sc) * (i[None, :] <= i[:, None])) @ vv[:, h // (heads // kvh)]
+            k = new[r]
+            w = max(w, _rel(out[at:at + k], ref.reshape(n, -1)[n - k:]))
+            at += k
+        worst.append(w)
+    return max(worst[0], worst[1] / 200), 1e-4                     # bfloat16 storage is held to 2e-2
+
+
+def check_gemm_tc_activation(dev) -> Tuple[float, float]:
+    """relu(x W^T)^2 and the tanh form of GELU in the tcgen05 product's epilogue, tokens and weights as the wide operand."""
+    from types import SimpleNamespace
+    from .kernels import fast, ops
+    worst = 0.0
+    ctx = SimpleNamespace(err=torch.zeros(1, dtype=torch.int32, device=dev))
+    for M, N, K in ((24, 512, 256), (384, 768, 512)):
+        x = torch.randn(M, K).to(torch.bfloat16)
+        w = (torch.randn(N, K) * 0.06).to(torch.bfloat16)
+        z = x.double() @ w.double().T
+        for name, want in (("relu2", torch.relu(z) ** 2),
+                           ("gelu_tanh", 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))))):
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            if not fast.linear_act_bf16(ctx, x.to(dev), w.to(dev), out, ops.ACTIVATIONS[name]):
+                raise RuntimeError("the tcgen05 product refused sizes it should take")
+            worst = max(worst, _rel(out, want))
+    if int(ctx.err.item()):
+        return float("inf"), 0.0
+    return worst, 2.0 ** -7
+
+
 CHECKS: List[Tuple[str, Callable]] = [
     ("embedding gather", check_embedding),
     ("rmsnorm + residual add", check_rmsnorm),
@@ -458,6 +550,8 @@ CHECKS: List[Tuple[str, Callable]] = [
     ("clamped gated unit, kernel and tcgen05 epilogue", check_clamped_unit),
     ("gated linear attention: decay, recurrence, norm and gate", check_linear_attention),
     ("differential attention, float32 and mma.sync", check_diff_attention),
+    ("attention without softmax, float32 and mma.sync", check_sigmoid_attention),
+    ("product, tcgen05 with an activation in the epilogue", check_gemm_tc_activation),
     ("sampling", check_sampling),
     ("largest logits of a row", check_largest_logits),
 ]
