@@ -348,7 +348,7 @@ def head_numbers(nh, seed):
 
 
 ATTN_SHAPES = [(3, 1, 12, 20, 8), (4, 2, 64, 32, 16), (2, 2, 130, 33, 24), (8, 1, 32, 32, 16), (16, 4, 64, 64, 16), (5, 5, 16, 128, 8),
-               (4, 4, 128, 128, 32)]
+               (4, 4, 128, 128, 32), (34, 2, 16, 24, 8)]           # the last: groups of 17 query heads, more than a product tile's rows
 
 
 @gpu
@@ -655,6 +655,18 @@ def test_long_decoding_over_many_steps_of_the_temperature(folders, dtype):
     s = random_tokens(330, cfg["vocab"], 8)
     got = run_schedule(eng, [s], [[(0, 10)]] + [[(0, 1)]] * 320)
     compare(got[0], cfg, W, s, dtype, "long decode")
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_then_single_tokens_in_an_engine_made_for_long_contexts(folders, dtype):
+    """700 tokens in one step (eleven row tiles, up to eleven key tiles each), then single tokens in an engine whose
+    longest context is 4,096, so the decode graph cuts every token's keys into several slices."""
+    folder, cfg, W, page = pick(folders, "g2", dtype)
+    eng = engine(folder, dtype, page, tokens=4096, batch=1024)
+    s = random_tokens(706, cfg["vocab"], 21)
+    got = run_schedule(eng, [s], [[(0, 700)]] + [[(0, 1)]] * 6)
+    compare(got[0], cfg, W, s, dtype, "long prompt")
 
 
 @gpu
