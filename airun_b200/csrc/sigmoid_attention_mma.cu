@@ -49,6 +49,45 @@ __device__ __forceinline__ float sam_log2(float x) {
     return r;
 }
 
+// ---- bulk copies (one instruction a row, carried out by the copy engine) and the barrier that counts their bytes
+__device__ __forceinline__ uint32_t sam_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void sam_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void sam_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void sam_mbar_arrive_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool sam_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false after about two seconds: the caller then gives up (all threads of the CTA together)
+__device__ __forceinline__ bool sam_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < 64; ++i)
+        if (sam_mbar_try(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (sam_mbar_try(bar, parity)) return true;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) return false;
+    }
+}
+// bytes: a multiple of 16; both addresses on 16-byte boundaries
+__device__ __forceinline__ void sam_bulk_row(void* smem, const void* gmem, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(sam_u32(smem)), "l"(gmem), "r"(bytes), "r"(bar) : "memory");
+}
+
 struct SamParams {
     const __nv_bfloat16* q;
     __nv_bfloat16* out;
@@ -138,7 +177,11 @@ struct SamLoader {
 // Prompt portions.  One CTA (4 warps) takes up to 64 consecutive tokens of one request and one query head; a warp
 // owns 16 of them.  The CTA finds its tile by walking the requests' token counts (cu_tokens), so the launch needs
 // nothing from the host but an upper bound of the tile count: ceil(T / 64) + requests.  The keys the tile can see
-// are walked in tiles of 64 through two asynchronous stages.
+// are walked in tiles of 64 through two stages.  With head sizes in multiples of 8 a stage is filled by bulk copies:
+// thread i asks for ONE row of the tile (key i of K, or key i - 64 of V: a page lookup and one instruction), and the
+// stage's mbarrier, on which every thread arrives with the bytes it has asked for, completes when all of them have
+// landed.  (Sixteen-byte cp.async pieces, sixteen a thread and tile, held all four warps up for as long as the copy
+// took to be accepted: copies and products ran one after the other.)  Other head sizes are copied element by element.
 template <int DP, int DVP>
 __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamParams p) {
     pdl_trigger();
@@ -149,6 +192,7 @@ __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamPar
     __nv_bfloat16* Ks0 = Qs + SAM_ROWS * QS;                                   // [2][64][QS]
     __nv_bfloat16* Vs0 = Ks0 + 2 * SAM_KEYS * QS;                              // [2][64][VS]
     float* tab = reinterpret_cast<float*>(Vs0 + 2 * SAM_KEYS * VS);            // [128]: a * log2(1 + b * d) by row - column + 63
+    const uint32_t bar0 = sam_u32(tab + 128);                                  // two mbarriers, one a stage
     // ---- which tile (tiles later in a request see more keys: the grid is walked from its end so that they start first)
     int b = gridDim.y - 1 - blockIdx.y, req = -1, first = 0, n = 0, p0 = 0;
     for (int r = 0; r < p.num_reqs; ++r) {
@@ -173,6 +217,15 @@ __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamPar
         uint4* z = reinterpret_cast<uint4*>(sam_smem);
         for (int e = tid; e < WORDS16; e += 128) z[e] = make_uint4(0u, 0u, 0u, 0u);
     }
+    const bool bulk = ld.vec;
+    if (bulk) {
+        if (tid == 0) {
+            sam_mbar_init(bar0, 128);
+            sam_mbar_init(bar0 + 8, 128);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the zeros, before the copy engine writes there
+    }
     __syncthreads();
     if (ld.vec) {
         const int per = D / 8;
@@ -180,6 +233,7 @@ __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamPar
             const int row = e / per, c = (e - row * per) * 8;
             sam_cp16(Qs + row * QS + c, p.q + ((size_t)(first + row) * p.nh + head) * D + c);
         }
+        sam_commit();
     } else {
         for (int e = tid; e < n * D; e += 128) {
             const int row = e / D, c = e - row * D;
@@ -203,24 +257,54 @@ __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamPar
     const bool has_dist = p.dist_a != nullptr;
     const float da = has_dist ? p.dist_a[head] : 0.0f, db = has_dist ? p.dist_b[head] : 0.0f;
     const float mul = -p.scale * SAM_LOG2E, add = p.head_c ? -p.head_c[head] * SAM_LOG2E : 0.0f;
-    ld.load(lo, hi, Ks0, Vs0);
+    // this thread's row of a tile: K of key tid (threads 0-63) or V of key tid - 64
+    const bool row_k = tid < SAM_KEYS;
+    const int row_key = tid & (SAM_KEYS - 1);
+    const uint32_t row_bytes = (uint32_t)(row_k ? D : Dv) * 2u;
+    const size_t row_off = row_k ? (size_t)kvh * p.page_size * D : (size_t)p.nkv * p.page_size * D + (size_t)kvh * p.page_size * Dv;
+    const size_t page_elems = (size_t)p.nkv * p.page_size * (D + Dv);
+    const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
+    bool bad_page = false, gave_up = false;
+    auto fill = [&](int kbase, int stage) {                // asks for the tile that begins at key kbase
+        if (!bulk) {
+            ld.load(kbase, hi, Ks0 + stage * SAM_KEYS * QS, Vs0 + stage * SAM_KEYS * VS);
+            return;
+        }
+        const int j = kbase + row_key, blk = j / p.page_size;
+        const int page = (j <= hi && blk < p.max_blocks) ? bt[blk] : -1;
+        if (j > hi) {
+            sam_mbar_arrive(bar0 + 8 * stage);
+        } else if (page < 0 || page >= p.num_pages) {
+            bad_page = true;
+            sam_mbar_arrive(bar0 + 8 * stage);
+        } else {
+            sam_mbar_arrive_tx(bar0 + 8 * stage, row_bytes);
+            __nv_bfloat16* dst = row_k ? Ks0 + (stage * SAM_KEYS + row_key) * QS : Vs0 + (stage * SAM_KEYS + row_key) * VS;
+            sam_bulk_row(dst, p.pool + (size_t)page * page_elems + row_off + (size_t)(j - blk * p.page_size) * (row_k ? D : Dv),
+                         row_bytes, bar0 + 8 * stage);
+        }
+    };
+    fill(lo, 0);
     int it = 0;
     for (int kbase = lo; kbase <= hi; kbase += SAM_KEYS, ++it) {
         const int buf = it & 1;
         const __nv_bfloat16* Ks = Ks0 + buf * SAM_KEYS * QS;
         const __nv_bfloat16* Vs = Vs0 + buf * SAM_KEYS * VS;
-        if (kbase + SAM_KEYS <= hi) {
-            ld.load(kbase + SAM_KEYS, hi, Ks0 + (buf ^ 1) * SAM_KEYS * QS, Vs0 + (buf ^ 1) * SAM_KEYS * VS);
-            sam_wait<1>();
-        } else {
-            sam_wait<0>();
+        if (kbase + SAM_KEYS <= hi) fill(kbase + SAM_KEYS, buf ^ 1);
+        bool landed = true;
+        if (bulk) {
+            if (it == 0) sam_wait<0>();                    // this thread's pieces of Q
+            landed = sam_mbar_wait(bar0 + 8 * buf, (uint32_t)(it >> 1) & 1u);
         }
         // the distance terms of this tile: its last readers passed the barrier that ended the tile before
         if (has_dist && tid < 127) {
             const int d = p0 - kbase + tid - 63;
             tab[tid] = d > 0 ? da * sam_log2(fmaf(db, (float)d, 1.0f)) : 0.0f;
         }
-        __syncthreads();
+        if (!__syncthreads_and(landed)) {                  // a copy that never came: every thread leaves here
+            gave_up = true;
+            break;
+        }
         if (warp * 16 < n) {                               // a warp without rows only helps to load
             float S[SAM_KEYS / 8][4];
 #pragma unroll
@@ -279,7 +363,11 @@ __global__ __launch_bounds__(128) void sigmoid_attention_mma_kernel(const SamPar
         }
         __syncthreads();                                   // this stage and the table may be written again
     }
-    if (ld.bad && lane == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
+    if ((ld.bad || bad_page) && lane == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
+    if (gave_up) {
+        if (tid == 0) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        return;
+    }
     if (warp * 16 >= n) return;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -324,6 +412,17 @@ __global__ __launch_bounds__(128) void sigmoid_attention_group_kernel(const SamP
         uint4* z = reinterpret_cast<uint4*>(sam_smem);
         for (int e = tid; e < WORDS16; e += 128) z[e] = make_uint4(0u, 0u, 0u, 0u);
     }
+    // the stages are filled by bulk copies, a row a thread, as in the tile kernel (head sizes in multiples of 8)
+    const bool bulk = ld.vec;
+    const uint32_t bar0 = sam_u32(Vs0 + 2 * SAM_KEYS * VS);                    // two mbarriers behind the stages
+    if (bulk) {
+        if (tid == 0) {
+            sam_mbar_init(bar0, 128);
+            sam_mbar_init(bar0 + 8, 128);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
     // this slice's key tiles
     const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
@@ -361,19 +460,51 @@ __global__ __launch_bounds__(128) void sigmoid_attention_group_kernel(const SamP
     for (int i = 0; i < DVP / 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) O[i][j] = 0.0f;
-    if (lo <= hi) ld.load(lo, hi, Ks0, Vs0);
+    const bool row_k = tid < SAM_KEYS;
+    const int row_key = tid & (SAM_KEYS - 1);
+    const uint32_t row_bytes = (uint32_t)(row_k ? D : Dv) * 2u;
+    const size_t row_off = row_k ? (size_t)kvh * p.page_size * D : (size_t)p.nkv * p.page_size * D + (size_t)kvh * p.page_size * Dv;
+    const size_t page_elems = (size_t)p.nkv * p.page_size * (D + Dv);
+    const int32_t* bt = p.block_table + (size_t)r * p.max_blocks;
+    bool bad_page = false, gave_up = false;
+    auto fill = [&](int kbase, int stage) {
+        if (!bulk) {
+            ld.load(kbase, hi, Ks0 + stage * SAM_KEYS * QS, Vs0 + stage * SAM_KEYS * VS);
+            return;
+        }
+        const int j = kbase + row_key, blk = j / p.page_size;
+        const int page = (j <= hi && blk < p.max_blocks) ? bt[blk] : -1;
+        if (j > hi) {
+            sam_mbar_arrive(bar0 + 8 * stage);
+        } else if (page < 0 || page >= p.num_pages) {
+            bad_page = true;
+            sam_mbar_arrive(bar0 + 8 * stage);
+        } else {
+            sam_mbar_arrive_tx(bar0 + 8 * stage, row_bytes);
+            __nv_bfloat16* dst = row_k ? Ks0 + (stage * SAM_KEYS + row_key) * QS : Vs0 + (stage * SAM_KEYS + row_key) * VS;
+            sam_bulk_row(dst, p.pool + (size_t)page * page_elems + row_off + (size_t)(j - blk * p.page_size) * (row_k ? D : Dv),
+                         row_bytes, bar0 + 8 * stage);
+        }
+    };
+    if (lo <= hi) {
+        if (bulk) sam_commit();                            // this thread's pieces of Q
+        fill(lo, 0);
+    }
     int it = 0;
     for (int kbase = lo; kbase <= hi; kbase += SAM_KEYS, ++it) {
         const int buf = it & 1;
         const __nv_bfloat16* Ks = Ks0 + buf * SAM_KEYS * QS;
         const __nv_bfloat16* Vs = Vs0 + buf * SAM_KEYS * VS;
-        if (kbase + SAM_KEYS <= hi) {
-            ld.load(kbase + SAM_KEYS, hi, Ks0 + (buf ^ 1) * SAM_KEYS * QS, Vs0 + (buf ^ 1) * SAM_KEYS * VS);
-            sam_wait<1>();
-        } else {
-            sam_wait<0>();
+        if (kbase + SAM_KEYS <= hi) fill(kbase + SAM_KEYS, buf ^ 1);
+        bool landed = true;
+        if (bulk) {
+            if (it == 0) sam_wait<0>();
+            landed = sam_mbar_wait(bar0 + 8 * buf, (uint32_t)(it >> 1) & 1u);
         }
-        __syncthreads();
+        if (!__syncthreads_and(landed)) {                  // a copy that never came: every thread leaves here
+            gave_up = true;
+            break;
+        }
         const int k0 = kbase + 16 * warp;                  // this warp's sixteen keys
         if (k0 <= hi) {
             float S[2][4];
@@ -419,7 +550,11 @@ __global__ __launch_bounds__(128) void sigmoid_attention_group_kernel(const SamP
         }
         __syncthreads();
     }
-    if (ld.bad && lane == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
+    if ((ld.bad || bad_page) && lane == 0) atomicOr(p.err, AIRUN_DEV_BAD_PAGE);
+    if (gave_up) {
+        if (tid == 0) atomicOr(p.err, AIRUN_DEV_TIMEOUT);
+        return;
+    }
     // ---- the four warps' sums into warp 0, in warp order (the stages are free: every copy has landed)
     sam_wait<0>();
     __syncthreads();
@@ -480,7 +615,7 @@ __global__ __launch_bounds__(256) void sam_reduce_kernel(const SamParams p) {
 
 template <int DP, int DVP>
 static int sag_launch(const SamParams& p, cudaStream_t stream) {
-    const size_t tiles = (size_t)((16 + 2 * SAM_KEYS) * (DP + SAM_PAD) + 2 * SAM_KEYS * (DVP + SAM_PAD)) * sizeof(__nv_bfloat16);
+    const size_t tiles = (size_t)((16 + 2 * SAM_KEYS) * (DP + SAM_PAD) + 2 * SAM_KEYS * (DVP + SAM_PAD)) * sizeof(__nv_bfloat16) + 16;
     const size_t merge = (size_t)128 * (DVP / 8 * 4 + 1) * sizeof(float);
     const size_t smem = tiles > merge ? tiles : merge;
     static unsigned long long configured = 0;
@@ -497,7 +632,7 @@ static int sag_launch(const SamParams& p, cudaStream_t stream) {
 
 template <int DP, int DVP>
 static int sam_launch(const SamParams& p, int max_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)(3 * SAM_ROWS * (DP + SAM_PAD) + 2 * SAM_KEYS * (DVP + SAM_PAD)) * sizeof(__nv_bfloat16) + 128 * sizeof(float);
+    const size_t smem = (size_t)(3 * SAM_ROWS * (DP + SAM_PAD) + 2 * SAM_KEYS * (DVP + SAM_PAD)) * sizeof(__nv_bfloat16) + 128 * sizeof(float) + 16;
     static unsigned long long configured = 0;
     if (smem > 48 * 1024 && first_on_device(configured)) {
         cudaError_t e = cudaFuncSetAttribute(sigmoid_attention_mma_kernel<DP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
