@@ -209,10 +209,11 @@ class CopyPlan:
 @dataclass(frozen=True)
 class CacheBinding:
     """Where one entry of the execution order finds its cache."""
-    kind: str            # "paged" | "state" | "none"
+    kind: str            # "paged" | "state" | "none" | "multi"
     gid: int
     index: int           # row of the group's tensor
     shared: bool         # True: reads another entry's cache and writes nothing
+    parts: Tuple["CacheBinding", ...] = ()     # "multi": an entry whose mixer keeps several caches (a tuple of specs)
 
 
 class CacheManager:
@@ -228,32 +229,39 @@ class CacheManager:
         self.paged: List[PagedGroup] = []
         self.state: List[StateGroup] = []
         self.bindings: List[CacheBinding] = []
+        def own(i: int, spec) -> CacheBinding:
+            if spec is None:
+                return CacheBinding("none", -1, -1, False)
+            if isinstance(spec, (tuple, list)):          # a mixer made of several: each half has a cache of its own
+                return CacheBinding("multi", -1, -1, False, tuple(own(i, s_) for s_ in spec))
+            if isinstance(spec, PagedKVSpec):
+                g = next((g for g in self.paged if g.spec == spec), None)
+                if g is None:
+                    g = PagedGroup(len(self.paged), spec, [], page_size)
+                    self.paged.append(g)
+                g.owners.append(i)
+                return CacheBinding("paged", g.gid, len(g.owners) - 1, False)
+            if isinstance(spec, StateSpec):
+                g = next((g for g in self.state if g.spec == spec), None)
+                if g is None:
+                    g = StateGroup(len(self.state), spec, [])
+                    self.state.append(g)
+                g.owners.append(i)
+                return CacheBinding("state", g.gid, len(g.owners) - 1, False)
+            raise TypeError(f"entry {i} has an unknown cache spec {spec!r}")
+
+        def reader(b: CacheBinding) -> CacheBinding:
+            return CacheBinding(b.kind, b.gid, b.index, True, tuple(reader(p) for p in b.parts))
+
         for i, (spec, src) in enumerate(zip(specs, cache_from)):
             if src is not None:
                 if not (0 <= src < i) or cache_from[src] is not None:
                     raise ValueError(f"entry {i} reads the cache of entry {src}, which must be an earlier owner")
                 if specs[src] != spec:
                     raise ValueError(f"entry {i} cannot read the cache of entry {src}: their cache specs differ")
-                b = self.bindings[src]
-                self.bindings.append(CacheBinding(b.kind, b.gid, b.index, True))
-            elif spec is None:
-                self.bindings.append(CacheBinding("none", -1, -1, False))
-            elif isinstance(spec, PagedKVSpec):
-                g = next((g for g in self.paged if g.spec == spec), None)
-                if g is None:
-                    g = PagedGroup(len(self.paged), spec, [], page_size)
-                    self.paged.append(g)
-                g.owners.append(i)
-                self.bindings.append(CacheBinding("paged", g.gid, len(g.owners) - 1, False))
-            elif isinstance(spec, StateSpec):
-                g = next((g for g in self.state if g.spec == spec), None)
-                if g is None:
-                    g = StateGroup(len(self.state), spec, [])
-                    self.state.append(g)
-                g.owners.append(i)
-                self.bindings.append(CacheBinding("state", g.gid, len(g.owners) - 1, False))
+                self.bindings.append(reader(self.bindings[src]))
             else:
-                raise TypeError(f"entry {i} has an unknown cache spec {spec!r}")
+                self.bindings.append(own(i, spec))
         self.max_blocks = int(max_blocks) if max_blocks else num_pages
         self._lib = _lib()
         n = len(self.paged)

@@ -5,6 +5,7 @@ from .qwen3 import Qwen3Config
 from .vedizen import VedizenConfig
 from .pogarax import PogaraxConfig
 from .gamanex import GamanexConfig
+from .tagulix import TagulixConfig
 
 
 def _register_builtin() -> None:
@@ -13,6 +14,7 @@ def _register_builtin() -> None:
     register_architecture("Vedizen", VedizenConfig, build_decoder)
     register_architecture("Pogarax", PogaraxConfig, build_decoder)
     register_architecture("Gamanex", GamanexConfig, build_decoder)
+    register_architecture("Tagulix", TagulixConfig, build_decoder)
 
 
 _register_builtin()

@@ -35,6 +35,7 @@ class LayerSpec:
     norm_args: Dict[str, Any]
     arrangement: str = "pre_norm"
     arrangement_args: Dict[str, Any] = field(default_factory=dict)      # constants of the arrangement itself
+    index: Optional[int] = None       # the number in the layer's tensor names when it is not its place in the list
 
 
 @dataclass(frozen=True)
@@ -78,6 +79,11 @@ class ModelConfig:
     def head(self) -> Tuple[str, dict]:
         """(registered name, constructor arguments) of the output head, e.g. ("lm_head", {"soft_cap": 30.0})."""
         return "lm_head", {}
+
+    def residual_streams(self) -> int:
+        """Copies of the residual a token carries through the layers (arrangements that declare ``multi_stream`` read
+        and write all of them); they start equal to the embedding and are summed in front of the final norm."""
+        return 1
 
 
 _REGISTRY: Dict[str, Tuple[type, Callable]] = {}

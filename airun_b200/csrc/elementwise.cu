@@ -623,7 +623,9 @@ AIRUN_EXPORT int airun_cast_f32(const float* in, void* out, int out_dtype, long 
 
 // out = f(in) element by element, in: float32 [T][n] -> out's type (rows of `out` may be strided).
 //   0: relu(z)^2   1: z * sigmoid(z)   2: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))   3: relu(z)
+//   4: 0.5 z (1 + erf(z / sqrt(2)))
 __device__ __forceinline__ float unit_act(float z, int mode) {
+    if (mode == 4) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
     if (mode == 0) { const float r = fmaxf(z, 0.0f); return r * r; }
     if (mode == 1) return z / (1.0f + expf(-z));
     if (mode == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -643,7 +645,7 @@ __global__ void act_kernel(const float* __restrict__ in, TOut* __restrict__ out,
 
 AIRUN_EXPORT int airun_act(const float* in, void* out, int out_dtype, int T, int n, long long out_stride, int mode,
                            cudaStream_t stream) {
-    if (T < 0 || n <= 0 || mode < 0 || mode > 3 || out_stride < n) return AIRUN_ERR_ARG;
+    if (T < 0 || n <= 0 || mode < 0 || mode > 4 || out_stride < n) return AIRUN_ERR_ARG;
     const long long total = (long long)T * n;
     if (total == 0) return AIRUN_OK;
     const long long blocks = (total + 255) / 256;

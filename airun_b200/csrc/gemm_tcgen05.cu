@@ -208,6 +208,7 @@ struct SmemLayout {
 
 // An activation of 16 results in place, for feed-forwards without a gate (out = f(x W^T)):
 //   m = 0: relu(z)^2   1: z * sigmoid(z)   2: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))   3: relu(z)
+//       4: 0.5 z (1 + erf(z / sqrt(2)))
 __device__ __forceinline__ void epilogue_act(float* v, int m) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -215,6 +216,7 @@ __device__ __forceinline__ void epilogue_act(float* v, int m) {
         if (m == 0) { const float r = fmaxf(z, 0.0f); v[i] = r * r; }
         else if (m == 1) v[i] = z / (1.0f + __expf(-z));
         else if (m == 2) v[i] = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        else if (m == 4) v[i] = 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
         else v[i] = fmaxf(z, 0.0f);
     }
 }
@@ -1093,9 +1095,25 @@ static int gemm_launch(const void* x, const void* W, void* out, int M, int N, in
 // The grouped product: rows seg[e] .. seg[e + 1] - 1 of x [M][K] times W[e] ([n_seg][N][K], contiguous) into the same
 // rows of out.  epi 0: float32 [M][N]; 1: bfloat16 [M][N]; 2: SwiGLU over interleaved gate/up rows, bfloat16 [M][N/2].
 // ``seg`` (int32 [n_seg + 1]) lives on the device; rows from seg[n_seg] on are left as they are.
+static int gemm_grouped(const void* x, const void* W, void* out, int M, int N, int K, long long ldx, long long ldc, int epi,
+                        const int32_t* seg, int n_seg, int* err, cudaStream_t stream, int act);
+
 AIRUN_EXPORT int airun_gemm_tcgen05_grouped(const void* x, const void* W, void* out, int M, int N, int K, long long ldx,
                                             long long ldc, int epi, const int32_t* seg, int n_seg, int* err,
                                             cudaStream_t stream) {
+    return gemm_grouped(x, W, out, M, N, K, ldx, ldc, epi, seg, n_seg, err, stream, 0);
+}
+
+// The grouped product with an activation f (mode 0..4, see epilogue_act) on the finished sums: out = f(x_e W_e^T).
+AIRUN_EXPORT int airun_gemm_tcgen05_grouped_act(const void* x, const void* W, void* out, int M, int N, int K, long long ldx,
+                                                long long ldc, int epi, const int32_t* seg, int n_seg, int mode, int* err,
+                                                cudaStream_t stream) {
+    if ((epi != EPI_F32 && epi != EPI_BF16) || mode < 0 || mode > 4) return AIRUN_ERR_ARG;
+    return gemm_grouped(x, W, out, M, N, K, ldx, ldc, epi, seg, n_seg, err, stream, 1 + mode);
+}
+
+static int gemm_grouped(const void* x, const void* W, void* out, int M, int N, int K, long long ldx, long long ldc, int epi,
+                        const int32_t* seg, int n_seg, int* err, cudaStream_t stream, int act) {
     if (M <= 0 || N <= 0 || K <= 0 || !err || !seg || n_seg <= 0) return M == 0 ? AIRUN_OK : AIRUN_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return AIRUN_ERR_ARG;
     if (epi == EPI_SWIGLU && (N % 32 != 0)) return AIRUN_ERR_ARG;
@@ -1111,6 +1129,7 @@ AIRUN_EXPORT int airun_gemm_tcgen05_grouped(const void* x, const void* W, void* 
     p.err = err;
     p.seg = seg;
     p.n_seg = n_seg;
+    p.act = act;
     CUtensorMap ma, mb;
     int r;
     if ((r = make_map(&ma, x, M, K, ldx, BM)) != AIRUN_OK) return r;
@@ -1146,7 +1165,7 @@ AIRUN_EXPORT int airun_gemm_tcgen05_glu(const void* x, const void* W, void* out,
 AIRUN_EXPORT int airun_gemm_tcgen05_act(const void* x, const void* W, void* out, int M, int N, int K,
                                         long long ldx, long long ldw, long long ldc, int epi, int swap, int bn, int ksplit,
                                         float* scratch, int* counters, int* err, cudaStream_t stream, int mode) {
-    if ((epi != EPI_F32 && epi != EPI_BF16) || mode < 0 || mode > 3) return AIRUN_ERR_ARG;
+    if ((epi != EPI_F32 && epi != EPI_BF16) || mode < 0 || mode > 4) return AIRUN_ERR_ARG;
     return gemm_launch(x, W, out, M, N, K, ldx, ldw, ldc, epi, swap, bn, ksplit, scratch, counters, err, stream,
                        nullptr, 0, 0, 0.0f, 0, nullptr, 0, nullptr, nullptr, 0, 0.0f, 0.0f, 1 + mode);
 }

@@ -111,12 +111,15 @@ __device__ __forceinline__ void gla_cp4(float* smem, const float* gmem) {
 __device__ __forceinline__ void gla_cp16(float* smem, const float* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
-template <int NS>
+// With CONST the decay is one number per head (`head_decay`), the same for every token and key channel, and nothing is
+// staged for it; `in_silu` applies z * sigmoid(z) to the staged q, k and v (projections that carry their activation).
+template <int NS, bool CONST>
 __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long row_stride,
     const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
     const int32_t* __restrict__ cu_tokens, const int32_t* __restrict__ state_slots, int max_slots,
-    float* __restrict__ out, int heads, int D, int Dv, float q_scale, int* __restrict__ err) {
+    float* __restrict__ out, int heads, int D, int Dv, float q_scale, int* __restrict__ err,
+    const float* __restrict__ head_decay, int in_silu) {
     pdl_trigger();
     pdl_wait();
     constexpr int DP = NS * GLA_WARPS;
@@ -143,6 +146,7 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     // 16-byte copies when every row begins on a 16-byte boundary
     const bool vec = (D % 4 == 0) && (Dv % 4 == 0) && (row_stride % 4 == 0) &&
                      ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay) & 15) == 0);
+    const float dec = CONST ? head_decay[blockIdx.y] : 0.0f;
     auto stage = [&](int base, int buf) {
         const int nt = min(GLA_TT, n - base);
         if (vec) {
@@ -152,7 +156,7 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
                 const size_t row = (size_t)(t0 + base + tt);
                 gla_cp16(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
                 gla_cp16(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
-                gla_cp16(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
+                if (!CONST) gla_cp16(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
             }
             for (int e = threadIdx.x; e < nt * nc4; e += 256) {
                 const int tt = e / nc4, c = (e - tt * nc4) * 4;
@@ -164,7 +168,7 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
                 const size_t row = (size_t)(t0 + base + tt);
                 gla_cp4(&s_q[buf][tt][d], q + row * row_stride + (size_t)head * D + d);
                 gla_cp4(&s_k[buf][tt][d], k + row * row_stride + (size_t)head * D + d);
-                gla_cp4(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
+                if (!CONST) gla_cp4(&s_a[buf][tt][d], decay + row * ((size_t)heads * D) + (size_t)head * D + d);
             }
             const int nc = min(GLA_COLS, Dv - col0);
             for (int e = threadIdx.x; e < nt * nc; e += 256) {
@@ -190,13 +194,25 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        if (in_silu) {
+            for (int e = threadIdx.x; e < nt * DP; e += 256) {
+                const float a = (&s_q[buf][0][0])[e], b = (&s_k[buf][0][0])[e];
+                (&s_q[buf][0][0])[e] = a / (1.0f + expf(-a));
+                (&s_k[buf][0][0])[e] = b / (1.0f + expf(-b));
+            }
+            for (int e = threadIdx.x; e < nt * GLA_COLS; e += 256) {
+                const float a = (&s_v[buf][0][0])[e];
+                (&s_v[buf][0][0])[e] = a / (1.0f + expf(-a));
+            }
+            __syncthreads();
+        }
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float vj = s_v[buf][tt][lane];
             float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
             for (int i4 = 0; i4 < NS / 4; ++i4) {
-                const float4 a4 = *reinterpret_cast<const float4*>(&s_a[buf][tt][d0 + 4 * i4]);
+                const float4 a4 = CONST ? make_float4(dec, dec, dec, dec) : *reinterpret_cast<const float4*>(&s_a[buf][tt][d0 + 4 * i4]);
                 const float4 k4 = *reinterpret_cast<const float4*>(&s_k[buf][tt][d0 + 4 * i4]);
                 const float4 q4 = *reinterpret_cast<const float4*>(&s_q[buf][tt][d0 + 4 * i4]);
                 S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * vj); acc0 = fmaf(S[4 * i4 + 0], q4.x, acc0);
@@ -223,24 +239,82 @@ __global__ __launch_bounds__(256) void gla_recurrent_kernel(
     }
 }
 
-AIRUN_EXPORT int airun_gla_recurrent(const float* q, const float* k, const float* v, long long row_stride,
-                                     const float* decay, float* state, long long slot_stride, int max_slots,
-                                     const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
-                                     float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
+static int gla_recurrent_launch(const float* q, const float* k, const float* v, long long row_stride,
+                                const float* decay, const float* head_decay, int in_silu, float* state, long long slot_stride,
+                                int max_slots, const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
+                                float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
     if (num_reqs < 0 || heads <= 0 || D <= 0 || D > 256 || Dv <= 0 || !state || !cu_tokens || !state_slots || !err ||
-        slot_stride < (long long)heads * D * Dv || heads > 65535)
+        slot_stride < (long long)heads * D * Dv || heads > 65535 || (!decay && !head_decay))
         return AIRUN_ERR_ARG;
     if (num_reqs == 0) return AIRUN_OK;
     const int tiles = ceil_div_i(Dv, GLA_COLS);
     if (tiles > 65535) return AIRUN_ERR_ARG;
     dim3 grid(num_reqs, heads, tiles);
-#define GLA_LAUNCH(NS) airun_launch(gla_recurrent_kernel<NS>, grid, dim3(256), 0, stream, q, k, v, row_stride, decay, state, \
-        slot_stride, cu_tokens, state_slots, max_slots, out, heads, D, Dv, q_scale, err)
-    if (D <= 32) GLA_LAUNCH(4);
-    else if (D <= 64) GLA_LAUNCH(8);
-    else if (D <= 128) GLA_LAUNCH(16);
-    else GLA_LAUNCH(32);
+#define GLA_LAUNCH(NS, C) airun_launch(gla_recurrent_kernel<NS, C>, grid, dim3(256), 0, stream, q, k, v, row_stride, decay, state, \
+        slot_stride, cu_tokens, state_slots, max_slots, out, heads, D, Dv, q_scale, err, head_decay, in_silu)
+#define GLA_PICK(C) do { if (D <= 32) GLA_LAUNCH(4, C); else if (D <= 64) GLA_LAUNCH(8, C); else if (D <= 128) GLA_LAUNCH(16, C); \
+        else GLA_LAUNCH(32, C); } while (0)
+    if (head_decay) GLA_PICK(true);
+    else GLA_PICK(false);
+#undef GLA_PICK
 #undef GLA_LAUNCH
+    return airun_launch_status();
+}
+
+AIRUN_EXPORT int airun_gla_recurrent(const float* q, const float* k, const float* v, long long row_stride,
+                                     const float* decay, float* state, long long slot_stride, int max_slots,
+                                     const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
+                                     float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
+    if (!decay) return AIRUN_ERR_ARG;
+    return gla_recurrent_launch(q, k, v, row_stride, decay, nullptr, 0, state, slot_stride, max_slots, cu_tokens, state_slots,
+                                num_reqs, out, heads, D, Dv, q_scale, err, stream);
+}
+
+// The same recurrence with ONE decay per head, S <- d_h S + k v^T, o = S^T q (times q_scale); `in_silu`: q, k and v
+// arrive without their activation z * sigmoid(z), which is applied as they are staged.
+AIRUN_EXPORT int airun_decay_recurrent(const float* q, const float* k, const float* v, long long row_stride,
+                                       const float* head_decay, int in_silu, float* state, long long slot_stride, int max_slots,
+                                       const int32_t* cu_tokens, const int32_t* state_slots, int num_reqs,
+                                       float* out, int heads, int D, int Dv, float q_scale, int* err, cudaStream_t stream) {
+    if (!head_decay) return AIRUN_ERR_ARG;
+    return gla_recurrent_launch(q, k, v, row_stride, nullptr, head_decay, in_silu, state, slot_stride, max_slots, cu_tokens,
+                                state_slots, num_reqs, out, heads, D, Dv, q_scale, err, stream);
+}
+
+// out[t][c] = scale * o[t][c] / sqrt(mean_c o[t]^2 + eps) * w[c] * sigmoid(gate[t][c]) over a token's whole row of n
+// numbers (all heads at once); one block per token.  o is float32 [T][n], gate float32 rows of `gate_stride`.
+template <typename TOut>
+__global__ __launch_bounds__(256) void rownorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                                           long long gate_stride, const float* __restrict__ w,
+                                                           TOut* __restrict__ out, long long out_stride, int n, float eps,
+                                                           float scale, const int32_t* __restrict__ req_of_token) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    if (req_of_token[t] < 0) return;
+    const float* orow = o + (size_t)t * n;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) ss = fmaf(orow[c], orow[c], ss);
+    ss = block_sum(ss, red);
+    const float inv = scale / sqrtf(ss / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + c])) : 1.0f;
+        out[(size_t)t * out_stride + c] = from_f32<TOut>(orow[c] * inv * (w ? w[c] : 1.0f) * g);
+    }
+}
+
+AIRUN_EXPORT int airun_rownorm_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out,
+                                    int out_dtype, long long out_stride, int T, int n, float eps, float scale,
+                                    const int32_t* req_of_token, cudaStream_t stream) {
+    if (T < 0 || n <= 0 || !o || !out || !req_of_token || out_stride < n || (gate && gate_stride < n)) return AIRUN_ERR_ARG;
+    if (T == 0) return AIRUN_OK;
+    if (out_dtype == AIRUN_DT_F32)
+        airun_launch(rownorm_gate_kernel<float>, dim3(T), dim3(256), 0, stream, o, gate, gate_stride, w, (float*)out, out_stride, n, eps, scale, req_of_token);
+    else if (out_dtype == AIRUN_DT_BF16)
+        airun_launch(rownorm_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, o, gate, gate_stride, w, (__nv_bfloat16*)out, out_stride, n, eps, scale, req_of_token);
+    else
+        return AIRUN_ERR_UNSUPPORTED;
     return airun_launch_status();
 }
 

@@ -57,13 +57,14 @@ class Workspace:
 @dataclass
 class CacheView:
     """The cache of one entry of the execution order, as its mixer sees it."""
-    kind: str                                   # "paged" | "state" | "none"
+    kind: str                                   # "paged" | "state" | "none" | "multi"
     shared: bool = False                        # reads another entry's cache, writes nothing
     pool: Optional[torch.Tensor] = None         # [pages, 2, kv_heads, page_size, head_dim]
     block_table: Optional[torch.Tensor] = None  # int32 [R, max_blocks]
     page_size: int = 0
     state: Optional[torch.Tensor] = None        # [max_requests, *shape]
     gid: int = -1
+    parts: Optional[List["CacheView"]] = None      # "multi": the caches of a mixer made of several, in its order
     shared_prefix: Optional[torch.Tensor] = None   # int32 [1] on the device: tokens at the start of every request of
                                                    # the batch that lie in the very same pages (0: none, or not known)
 

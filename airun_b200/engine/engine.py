@@ -124,6 +124,10 @@ class Engine:
         from ..parts.base import PagedKVSpec, StateSpec
         dt = _DTYPES[o.dtype]
         esz = 2 if dt == torch.bfloat16 else 4
+        flat = []                        # a mixer made of several keeps a tuple of specs
+        for s, src in zip(specs, cache_from):
+            flat += [(p, src) for p in (s if isinstance(s, (tuple, list)) else (s,))]
+        specs, cache_from = [p for p, _ in flat], [src for _, src in flat]
         per_token = sum(s.elements_per_token() * esz
                         for s, src in zip(specs, cache_from) if isinstance(s, PagedKVSpec) and src is None)
         if per_token == 0:

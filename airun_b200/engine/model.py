@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config.base import LayerCall, ModelConfig
-from ..parts.base import CastActivations, make_part, part_factory
+from ..parts.base import CastActivations, StreamWrite, make_part, part_factory
 from ..parts import embedding as _embedding_parts      # noqa: F401  (registers the embedding and head parts)
 from ..weights.loader import (DictSource, TensorSource, WeightSpec, load_tensors, random_tensors)
 
@@ -46,7 +46,7 @@ class DecoderModel:
                                    dtype=dtype, device=self.device, **emb_args)
         self.layers = []
         for i, spec in enumerate(config.layer_specs()):
-            p = names["layer"].format(i=i)
+            p = names["layer"].format(i=i if getattr(spec, "index", None) is None else spec.index)
             common = dict(dtype=dtype, device=self.device)
             norm1 = make_part("norm", spec.norm, prefix=f"{p}.{names['norm1']}", **spec.norm_args, **common)
             # an arrangement with one norm (``num_norms = 1``) gets no second one; a layer without a
@@ -61,6 +61,12 @@ class DecoderModel:
                 if spec.feed_forward else None
             self.layers.append(make_part("arrangement", spec.arrangement, norm1=norm1, mixer=mixer,
                                          norm2=norm2, ffn=ffn, dtype=dtype, **getattr(spec, "arrangement_args", {})))
+        # a residual of several streams: every layer's arrangement must read and write all of them
+        self.multi_stream = bool(self.layers) and all(getattr(l, "multi_stream", False) for l in self.layers)
+        if not self.multi_stream and any(getattr(l, "multi_stream", False) for l in self.layers):
+            raise ValueError("arrangements over several residual streams cannot be mixed with arrangements over one")
+        self.streams = int(getattr(config, "residual_streams", lambda: 1)()) if self.multi_stream else 1
+        self._stream_ones = torch.ones(self.streams, dtype=torch.float32, device=self.device)      # the read that sums the streams
         self.order: List[LayerCall] = list(config.execution_order())
         for c in self.order:
             if not (0 <= c.layer < len(self.layers)):
@@ -206,6 +212,8 @@ class DecoderModel:
         ctx.ws_main.reset()
         x = ctx.ws_main.alloc((T, self.H), torch.float32)
         self.embedding.forward(ctx, ctx.token_ids[:T], x)
+        if self.multi_stream:
+            return self._forward_streams(ctx, x, want_rows, n_want)
         delta = None
         trace = TRACE_LAYERS and not torch.cuda.is_current_stream_capturing()
         for ci, call in enumerate(self.order):
@@ -242,6 +250,42 @@ class DecoderModel:
         if isinstance(delta, CastActivations):
             delta = None
         self.final_norm.forward(ctx, x, hsel, delta=delta, rows=want_rows[:n_want])
+        logits = ctx.ws_main.alloc((n_want, self.V), torch.float32)
+        self.head.forward(ctx, hsel, logits)
+        return logits
+
+
+    def _forward_streams(self, ctx, x: torch.Tensor, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
+        """The pass over the layers with a residual of ``streams`` copies, [T, S, H]: every copy starts as the embedding,
+        each block leaves its last write pending for the next pass over the streams (parts/block.py:
+        HyperConnectionBlock), and the last pass writes it and sums the streams into x for the final norm."""
+        from ..kernels import ops
+        T, S = ctx.num_tokens, self.streams
+        xs = ctx.ws_main.alloc((T, S, self.H), torch.float32)
+        ops.stream_fill(x, xs)
+        pending = None
+        for ci, call in enumerate(self.order):
+            ctx.ws = ctx.ws_pair[ci % 2]
+            ctx.ws.reset()
+            if getattr(call, "add_row", None) is not None:
+                raise ValueError("rows of an order table are not added to a residual of several streams")
+            pending = self.layers[call.layer].forward(ctx, xs, pending, ctx.caches[ci])
+            if self.layer_hook is not None and not torch.cuda.is_current_stream_capturing():
+                now = xs[:T]
+                if isinstance(pending, StreamWrite):
+                    y = pending.y[:T] + (pending.y_bias if pending.y_bias is not None else 0.0)
+                    now = torch.einsum("st,jsw->jtw", pending.carry, now) + pending.mult * pending.write[None, :, None] * y[:, None, :]
+                self.layer_hook(ci, now.sum(dim=1))
+        if n_want == 0:
+            return None
+        p = pending
+        ops.stream_step(xs, y=p.y if p else None, carry=p.carry if p else None, write=p.write if p else None,
+                        mult=p.mult if p else 1.0, y_bias=p.y_bias if p else None, read=self._stream_ones, out=x,
+                        req_of_token=ctx.req_of_token)
+        ctx.ws = ctx.ws_pair[len(self.order) % 2]
+        ctx.ws.reset()
+        hsel = ctx.ws.alloc((n_want, self.H), self.dtype)
+        self.final_norm.forward(ctx, x, hsel, rows=want_rows[:n_want])
         logits = ctx.ws_main.alloc((n_want, self.V), torch.float32)
         self.head.forward(ctx, hsel, logits)
         return logits

@@ -98,17 +98,17 @@ class StepRunner:
         return (self.meta_dev if dev else self.meta_np)[off:off + n]
 
     def _cache_views(self) -> List[CacheView]:
-        views = []
-        for b in self.manager.bindings:
+        def view(b) -> CacheView:
             if b.kind == "paged":
                 bt = self._view(f"bt{b.gid}").view(self.R_max, self.max_blocks)
-                views.append(CacheView("paged", b.shared, self.storage.paged[b.gid][b.index], bt,
-                                       self.manager.page_size, gid=b.gid, shared_prefix=self._view(f"shared{b.gid}")))
-            elif b.kind == "state":
-                views.append(CacheView("state", b.shared, state=self.storage.state[b.gid][b.index], gid=b.gid))
-            else:
-                views.append(CacheView("none"))
-        return views
+                return CacheView("paged", b.shared, self.storage.paged[b.gid][b.index], bt,
+                                 self.manager.page_size, gid=b.gid, shared_prefix=self._view(f"shared{b.gid}"))
+            if b.kind == "state":
+                return CacheView("state", b.shared, state=self.storage.state[b.gid][b.index], gid=b.gid)
+            if b.kind == "multi":
+                return CacheView("multi", b.shared, parts=[view(p) for p in b.parts])
+            return CacheView("none")
+        return [view(b) for b in self.manager.bindings]
 
     def check_entries(self, entries: Sequence[StepEntry]) -> None:
         if not entries:

@@ -225,8 +225,10 @@ def linear_swiglu_bf16(ctx, x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tens
 GROUPED_MAX_TILES = 1024
 
 
-def grouped_linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor, swiglu_group: int = 0) -> bool:
+def grouped_linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, seg: torch.Tensor, swiglu_group: int = 0,
+                        act: Optional[int] = None) -> bool:
     """Rows seg[e] .. seg[e+1]-1 of x [M, K] times w[e]^T (w [E, N, K]) on tcgen05, the segments read from the device.
+    ``act`` (an ``ops.ACT_*``; not with ``swiglu_group``): the activation applied to the finished sums in the epilogue.
     ``swiglu_group`` 16: the rows of w[e] alternate between blocks of 16 gate and 16 up rows and out is the gated
     unit's result, bfloat16 [M, N/2]; 0: out [M, N] float32 or bfloat16.  False when the kernel does not take the
     sizes (the caller then uses the plain grouped product)."""
@@ -246,6 +248,14 @@ def grouped_linear_bf16(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor
     _cuda(x, w, out, seg)
     _need(out.stride(1) == 1 and seg.dtype == torch.int32 and seg.numel() >= E + 1 and seg.is_contiguous(),
           "out must be row-major and seg int32 [E + 1]")
+    if act is not None and not swiglu_group:
+        f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_grouped_act",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p,
+                 c_void_p])
+        _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),
+                 out.stride(0) if M > 1 else max(out.shape[1], out.stride(0)), epi, _p(seg), E, int(act), _p(ctx.err), _stream()),
+               "gemm_tcgen05_grouped_act")
+        return True
     f = _fn("gemm_tcgen05", "airun_gemm_tcgen05_grouped",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_p(x), _p(w), _p(out), M, N, K, x.stride(0) if M > 1 else max(K, x.stride(0)),

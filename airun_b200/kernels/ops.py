@@ -89,7 +89,8 @@ def required_libraries(dtype: torch.dtype, head_dim: int):
     """(name, defines) of every library a model of this dtype and head size uses."""
     libs = [("elementwise", None), ("gemm_simt", None), ("qkv_post", None),
             ("attention_generic", None), ("sampling", None), ("linear_attention", None), ("diff_attention", None),
-            ("recurrent_state", None), ("latent_attention", None), ("moe", None), ("sigmoid_attention", None)]
+            ("recurrent_state", None), ("latent_attention", None), ("moe", None), ("sigmoid_attention", None),
+            ("streams", None), ("softmax_attention", None)]
     return libs
 
 
@@ -284,12 +285,12 @@ def rmsnorm_pair(x: torch.Tensor, w1: torch.Tensor, out1: torch.Tensor, w2: torc
              1 if delta is not None else 0, _stream()), "rmsnorm_pair")
 
 
-ACT_RELU2, ACT_SILU, ACT_GELU_TANH, ACT_RELU = 0, 1, 2, 3
-ACTIVATIONS = {"relu2": ACT_RELU2, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu": ACT_RELU}
+ACT_RELU2, ACT_SILU, ACT_GELU_TANH, ACT_RELU, ACT_GELU_ERF = 0, 1, 2, 3, 4
+ACTIVATIONS = {"relu2": ACT_RELU2, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu": ACT_RELU, "gelu_erf": ACT_GELU_ERF}
 
 
 def act(src: torch.Tensor, out: torch.Tensor, mode: int) -> None:
-    """out = f(src) element by element: relu(z)^2, z sigmoid(z), the tanh form of GELU or relu(z) (``ACT_*``); src
+    """out = f(src) element by element: relu(z)^2, z sigmoid(z), the tanh or the erf form of GELU or relu(z) (``ACT_*``); src
     float32 [T, n], out [T, n] in its own type (a column slice of a wider buffer is fine)."""
     _cuda(src, out)
     _need(src.dtype == torch.float32 and src.dim() == 2 and src.is_contiguous(), "src must be contiguous float32 [T, n]")
@@ -386,6 +387,55 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torc
              c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(f(_p(q), _p(k), _p(v), stride, _p(decay), _p(state), state.stride(0), state.shape[0], _p(cu_tokens),
              _p(state_slots), int(num_reqs), _p(out), heads, D, Dv, float(q_scale), _p(err), _stream()), "gla_recurrent")
+
+
+def decay_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_decay: torch.Tensor, in_silu: bool,
+                    state: torch.Tensor, cu_tokens: torch.Tensor, state_slots: torch.Tensor, num_reqs: int, out: torch.Tensor,
+                    heads: int, D: int, Dv: int, q_scale: float, err: torch.Tensor) -> None:
+    """The recurrence with one decay per head, S <- d_h S + k v^T, o = S^T q * q_scale, for the tokens of every request in
+    order.  ``q``, ``k`` [T, heads*D] and ``v`` [T, heads*Dv] are float32 column slices of ONE buffer; with ``in_silu``
+    they arrive without their activation z sigmoid(z), which the kernel applies.  ``head_decay`` float32 [heads];
+    ``state`` [slots, heads, D, Dv] float32, updated in place; ``out`` float32 [T, heads*Dv]."""
+    _cuda(q, k, v, head_decay, state, cu_tokens, state_slots, out, err)
+    for t, w, name in ((q, heads * D, "q"), (k, heads * D, "k"), (v, heads * Dv, "v")):
+        _rows_f32(t, name)
+        _need(t.shape[1] == w, f"{name} must have {w} columns")
+    T = q.shape[0]
+    _need((q.stride(0) == k.stride(0) == v.stride(0)) or T <= 1, "q, k and v must share a row stride")
+    _need(head_decay.dtype == torch.float32 and head_decay.numel() == heads and head_decay.is_contiguous(),
+          "head_decay must be float32 [heads]")
+    _need(state.dtype == torch.float32 and state.dim() == 4 and tuple(state.shape[1:]) == (heads, D, Dv)
+          and state[0].is_contiguous(), "state must be float32 [slots, heads, D, Dv]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (T, heads * Dv) and out.is_contiguous(), "out must be float32 [T, heads*Dv]")
+    _need(cu_tokens.dtype == torch.int32 and cu_tokens.numel() >= num_reqs + 1 and state_slots.dtype == torch.int32
+          and state_slots.numel() >= num_reqs, "cu_tokens / state_slots must be int32 [R + 1] / [R]")
+    _need(D <= 256, f"{D} key channels a head are above the kernel's limit of 256")
+    stride = q.stride(0) if T > 1 else max(q.stride(0), k.stride(0), v.stride(0))
+    f = _fn("linear_attention", "airun_decay_recurrent",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(k), _p(v), stride, _p(head_decay), 1 if in_silu else 0, _p(state), state.stride(0), state.shape[0],
+             _p(cu_tokens), _p(state_slots), int(num_reqs), _p(out), heads, D, Dv, float(q_scale), _p(err), _stream()),
+           "decay_recurrent")
+
+
+def rownorm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+                 req_of_token: torch.Tensor, scale: float = 1.0) -> None:
+    """out = scale * o / rms(o) * weight * sigmoid(gate), the root mean square over a token's WHOLE row (all heads at
+    once).  ``o`` float32 [T, n] contiguous, ``gate`` float32 rows (a column slice is fine), ``out`` [T, n] rows."""
+    _cuda(o, gate, weight, out, req_of_token)
+    T, n = o.shape
+    _need(o.dtype == torch.float32 and o.is_contiguous(), "o must be contiguous float32 [T, n]")
+    if gate is not None:
+        _rows_f32(gate, "gate")
+        _need(tuple(gate.shape) == (T, n), "gate must be [T, n]")
+    if weight is not None:
+        _need(weight.dtype == torch.float32 and weight.numel() == n and weight.is_contiguous(), "the norm weight must be float32 [n]")
+    _need(tuple(out.shape) == (T, n) and out.stride(1) == 1, "out must be row-major [T, n]")
+    f = _fn("linear_attention", "airun_rownorm_gate",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(o), _p(gate), _row_stride(gate) if gate is not None else n, _p(weight), _p(out), _dt(out), _row_stride(out), T, n,
+             float(eps), float(scale), _p(req_of_token), _stream()), "rownorm_gate")
 
 
 GATE_SILU, GATE_SIGMOID, GATE_AS_IS = 0, 1, 2
@@ -558,6 +608,120 @@ def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, cache, ctx, nh: int, n
 
 
 # ---------------------------------------------------------------- matrix products
+# ---------------------------------------------------------------- a residual of several streams
+STREAMS_MAX = 8
+
+
+def stream_fill(x: torch.Tensor, xs: torch.Tensor) -> None:
+    """xs[t, s] = x[t] for every stream s: x float32 [T, H], xs float32 [T, S, H]."""
+    _cuda(x, xs)
+    T, S, H = xs.shape
+    _need(x.dtype == torch.float32 and xs.dtype == torch.float32 and tuple(x.shape) == (T, H) and x.is_contiguous()
+          and xs.is_contiguous(), "x / xs must be contiguous float32 [T, H] / [T, S, H]")
+    f = _fn("streams", "airun_stream_fill", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(xs), T, S, H, _stream()), "stream_fill")
+
+
+def stream_step(xs: torch.Tensor, y: Optional[torch.Tensor] = None, carry: Optional[torch.Tensor] = None,
+                write: Optional[torch.Tensor] = None, mult: float = 1.0, y_bias: Optional[torch.Tensor] = None,
+                read: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                out: Optional[torch.Tensor] = None, req_of_token: Optional[torch.Tensor] = None) -> None:
+    """One pass over the streams xs float32 [T, S, H] (csrc/streams.cu).  With ``y`` [T, H] the result of a sub-layer is
+    written in: x_t <- sum_s carry[s, t] x_s + mult * write[t] * (y + y_bias), all t from the old streams, in place.
+    With ``read`` [S] the next sub-layer's input is formed from the new streams: u = sum_s read[s] x_s, and
+    ``out`` = u / rms(u) * norm_w in out's type, or u itself in float32 when there is no ``norm_w``."""
+    _cuda(xs, y, carry, write, y_bias, read, norm_w, out, req_of_token)
+    _need(xs.dtype == torch.float32 and xs.dim() == 3 and xs.is_contiguous(), "xs must be contiguous float32 [T, S, H]")
+    T, S, H = xs.shape
+    _need(S <= STREAMS_MAX, f"{S} streams are above the kernel's limit of {STREAMS_MAX}")
+    _need(y is not None or read is not None, "nothing to do: neither a result to write nor a read")
+    if y is not None:
+        _rows_f32(y, "y")
+        _need(tuple(y.shape) == (T, H), "y must be [T, H]")
+        _need(carry is not None and write is not None and carry.dtype == torch.float32 and write.dtype == torch.float32
+              and carry.numel() == S * S and write.numel() == S and carry.is_contiguous() and write.is_contiguous(),
+              "carry / write must be float32 [S, S] / [S]")
+        if y_bias is not None:
+            _need(y_bias.dtype == torch.float32 and y_bias.numel() == H and y_bias.is_contiguous(), "y_bias must be float32 [H]")
+    if read is not None:
+        _need(read.dtype == torch.float32 and read.numel() == S and read.is_contiguous(), "read must be float32 [S]")
+        _need(out is not None and tuple(out.shape) == (T, H) and out.stride(1) == 1, "out must be row-major [T, H]")
+        if norm_w is None:
+            _need(out.dtype == torch.float32, "without a norm the weighted sum is stored in float32")
+        else:
+            _need(norm_w.dtype == torch.float32 and norm_w.numel() == H and norm_w.is_contiguous(), "norm_w must be float32 [H]")
+    f = _fn("streams", "airun_stream_step",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float,
+             c_void_p, c_int, c_longlong, c_void_p, c_void_p])
+    _check(f(_p(xs), T, S, H, _p(y), _row_stride(y) if y is not None else H, _p(y_bias), _p(carry), _p(write), float(mult), _p(read),
+             _p(norm_w), float(eps), _p(out), _dt(out) if out is not None else DT_F32, _row_stride(out) if out is not None else H,
+             _p(req_of_token), _stream()), "stream_step")
+
+
+# ---------------------------------------------------------------- softmax attention with its options
+def qkv_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                unit_norm: bool, eps: float, rope_kind: int, rotary_dim: int, inv_freq: Optional[torch.Tensor],
+                temp_coef: float, temp_every: int, q_out: torch.Tensor, cache, ctx, nh: int, nkv: int, D: int, Dv: int,
+                store: bool = True, rope_positions: Optional[torch.Tensor] = None) -> None:
+    """What lies between the q/k/v product and the attention (csrc/softmax_attention.cu: qkv_prepare_kernel): biases,
+    a weighted root-mean-square norm per head before the rotation (``q_w`` / ``k_w`` float32 [D]), the rotation, an
+    unweighted norm per head after it (``unit_norm``), the query temperature; q out, k and v into the token's page.
+    ``proj`` float32 rows [q heads | k heads | v heads] (q heads only without ``store``)."""
+    _cuda(proj, bias, q_w, k_w, inv_freq, q_out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, ctx.err, rope_positions)
+    _rows_f32(proj, "proj")
+    T = proj.shape[0]
+    width = nh * D + (nkv * (D + Dv) if store else 0)
+    _need(proj.shape[1] >= width, f"proj must have at least {width} columns")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, nh * D), "q_out must be contiguous [T, heads*D]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() >= width and bias.is_contiguous(), "the biases must be float32 [q | k | v]")
+    for w_ in (q_w, k_w):
+        _need(w_ is None or (w_.dtype == torch.float32 and w_.numel() == D and w_.is_contiguous()), "a q/k norm weight must be float32 [D]")
+    _need(D <= 256, "head sizes above 256 are beyond the kernel")
+    pool, bt = cache.pool, cache.block_table
+    if store:
+        _need(pool.dtype == q_out.dtype and pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (D + Dv),
+              "the cache pages do not fit the head sizes or the type of q")
+    f = _fn("softmax_attention", "airun_qkv_prepare",
+            [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_void_p, c_void_p])
+    _check(f(_p(proj), _row_stride(proj), _p(bias), _p(q_w), _p(k_w), 1 if unit_norm else 0, float(eps), int(rope_kind),
+             int(rotary_dim), _p(inv_freq), _p(rope_positions), float(temp_coef), int(temp_every), _p(q_out), _p(pool), _dt(q_out),
+             _p(bt), bt.stride(0), _p(ctx.positions), _p(ctx.req_of_token), T, int(ctx.num_reqs), pool.shape[0],
+             int(cache.page_size), nh, nkv, D, Dv, 1 if store else 0, _p(ctx.err), _stream()), "qkv_prepare")
+
+
+def softmax_attention(q: torch.Tensor, out: torch.Tensor, cache, ctx, nh: int, nkv: int, D: int, Dv: int, scale: float,
+                      table: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
+                      out_scale: float = 1.0) -> None:
+    """Softmax attention over cache pages in float32 arithmetic (csrc/softmax_attention.cu: softmax_attention_kernel):
+    ``table`` float32 [heads, n] adds table[h, min(i - j, n - 1)] to the scaled score, ``sink`` float32 [heads] adds
+    exp(sink_h) to the denominator, ``window`` > 0 hides keys with i - j >= window; the result is times ``out_scale``.
+    ``out`` may be a column slice of a wider buffer."""
+    _cuda(q, out, cache.pool, cache.block_table, ctx.positions, ctx.req_of_token, ctx.err, table, sink)
+    T = q.shape[0]
+    _need(q.is_contiguous() and tuple(q.shape) == (T, nh * D), "q must be contiguous [T, heads*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == q.dtype, "out must be row-major [T, heads*Dv] of q's type")
+    pool, bt = cache.pool, cache.block_table
+    _need(pool.dtype == q.dtype and pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (D + Dv),
+          "the cache pages do not fit the head sizes or the type of q")
+    table_len = 0
+    if table is not None:
+        _need(table.dtype == torch.float32 and table.dim() == 2 and table.shape[0] == nh and table.is_contiguous(),
+              "the distance table must be float32 [heads, n]")
+        table_len = table.shape[1]
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == nh and sink.is_contiguous(), "the sinks must be float32 [heads]")
+    f = _fn("softmax_attention", "airun_softmax_attention",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _row_stride(out), _p(pool), _dt(q), _p(bt), bt.stride(0), _p(ctx.positions), _p(ctx.req_of_token), T,
+             int(ctx.num_reqs), pool.shape[0], int(cache.page_size), nh, nkv, D, Dv, float(scale), _p(table), int(table_len),
+             _p(sink), int(window), float(out_scale), _p(ctx.err), _stream()), "softmax_attention")
+
+
+# ---------------------------------------------------------------- products
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores, float32 accumulation."""
     _cuda(a, w, out)
@@ -788,28 +952,63 @@ def moe_route(logits: torch.Tensor, top: int, softmax_scores: bool, renorm: bool
              _p(ids), _p(wts), _p(rank), _p(counts), _p(seg), _stream()), "moe_route")
 
 
-def moe_scatter(h: torch.Tensor, top: int, ids, wts, rank, seg, scale_input: bool, xs: torch.Tensor, row_of: torch.Tensor) -> None:
+def moe_scatter(h: torch.Tensor, top: int, ids, wts, rank, seg, scale_input: bool, xs: torch.Tensor, row_of: torch.Tensor,
+                num_real: int = 1 << 30) -> None:
     """xs[seg[e] + rank] = h[t] (times the weight with ``scale_input``) for each of the token's experts; row_of [T, top]
-    keeps the row."""
+    keeps the row (-1 for an expert id of ``num_real`` or more: an expert without matrices, which gets no row)."""
     _cuda(h, xs, row_of)
     T, W = h.shape
     _need(h.is_contiguous() and xs.is_contiguous() and tuple(xs.shape) == (T * top, W) and xs.dtype == h.dtype,
           "xs must be contiguous [T*top, W] of h's type")
     _need(row_of.dtype == torch.int32 and row_of.numel() >= T * top, "row_of must be int32 [T, top]")
     f = _fn("moe", "airun_moe_scatter",
-            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_p(h), _dt(h), T, W, int(top), _p(ids), _p(wts), _p(rank), _p(seg), 1 if scale_input else 0, _p(xs), _p(row_of),
-             _stream()), "moe_scatter")
+             int(num_real), _stream()), "moe_scatter")
 
 
-def moe_combine(ys: torch.Tensor, top: int, ids, wts, row_of, scale_output: bool, out: torch.Tensor) -> None:
-    """out[t] = sum over the token's experts, in the order chosen, of ys[row] (times the weight with ``scale_output``)."""
-    _cuda(ys, out)
+def moe_combine(ys: torch.Tensor, top: int, ids, wts, row_of, scale_output: bool, out: torch.Tensor,
+                passthrough: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum over the token's experts, in the order chosen, of ys[row] (times the weight with ``scale_output``);
+    an expert without a row (row_of -1) contributes ``passthrough[t]``, the feed-forward's own input [T, W]."""
+    _cuda(ys, out, passthrough)
+    if passthrough is not None:
+        _need(tuple(passthrough.shape) == tuple(out.shape) and passthrough.is_contiguous(), "passthrough must be contiguous [T, W]")
     T, W = out.shape
     _need(ys.dtype == torch.float32 and ys.is_contiguous() and tuple(ys.shape) == (T * top, W) and out.dtype == torch.float32
           and out.is_contiguous(), "ys / out must be contiguous float32 [T*top, W] / [T, W]")
-    f = _fn("moe", "airun_moe_combine", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
-    _check(f(_p(ys), T, W, int(top), _p(ids), _p(wts), _p(row_of), 1 if scale_output else 0, _p(out), _stream()), "moe_combine")
+    f = _fn("moe", "airun_moe_combine", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                         c_void_p])
+    _check(f(_p(ys), T, W, int(top), _p(ids), _p(wts), _p(row_of), 1 if scale_output else 0, _p(out), _p(passthrough),
+             _dt(passthrough) if passthrough is not None else DT_F32, _stream()), "moe_combine")
+
+
+def moe_route_grouped(logits: torch.Tensor, num_real: int, top: int, groups: int, keep: int, weight_scale: float,
+                      correction: Optional[torch.Tensor], req_of_token: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
+                      rank: torch.Tensor, counts: torch.Tensor, seg: torch.Tensor) -> None:
+    """Routing by softmax scores with a correction and groups (csrc/moe.cu: moe_route_grouped_kernel).  ``logits``
+    float32 [T, n_out]: the first ``num_real`` outputs are experts with matrices, the rest return their input.  Scores
+    are the softmax over all outputs; the choice is by score + ``correction`` inside the ``keep`` best of ``groups``
+    equal runs of neighbouring outputs; weights are the chosen scores over their sum (+ 1e-20) times ``weight_scale``.
+    ``counts`` (int32 [num_real]) must be zero on entry; seg [num_real + 1]."""
+    _cuda(logits, correction, req_of_token, ids, wts, rank, counts, seg)
+    _rows_f32(logits, "logits")
+    T, n_out = logits.shape
+    _need(n_out <= 1024 and 1 <= num_real <= n_out, "1 to 1024 router outputs, at least one expert with matrices")
+    _need(groups >= 1 and n_out % groups == 0 and 1 <= keep <= groups and 1 <= top <= (n_out // groups) * keep,
+          "the groups must divide the router's outputs and hold at least ``top`` of them")
+    for t_, dt in ((ids, torch.int32), (wts, torch.float32), (rank, torch.int32)):
+        _need(t_.dtype == dt and t_.numel() >= T * top and t_.is_contiguous(), "ids / wts / rank must be [T, top]")
+    _need(counts.dtype == torch.int32 and counts.numel() >= num_real and seg.dtype == torch.int32 and seg.numel() >= num_real + 1,
+          "counts / seg must be int32 [experts] / [experts + 1]")
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.numel() == n_out and correction.is_contiguous(),
+              "the correction must be float32 [router outputs]")
+    f = _fn("moe", "airun_moe_route_grouped",
+            [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p])
+    _check(f(_p(logits), _row_stride(logits), _p(correction), T, n_out, int(num_real), int(top), int(groups), int(keep),
+             float(weight_scale), _p(req_of_token), _p(ids), _p(wts), _p(rank), _p(counts), _p(seg), _stream()), "moe_route_grouped")
 
 
 # ---------------------------------------------------------------- attention

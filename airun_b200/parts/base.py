@@ -105,6 +105,18 @@ class CastActivations:
 
 
 @dataclass
+class StreamWrite:
+    """What a block over a residual of several streams leaves pending: the result ``y`` [T, H] of its last sub-layer
+    and the numbers that write it into the streams, x_t <- sum_s carry[s, t] x_s + mult * write[t] * (y + y_bias); the
+    next pass over the streams (the next block's read, or the sum at the end of the model) carries it out."""
+    y: torch.Tensor
+    carry: torch.Tensor
+    write: torch.Tensor
+    mult: float
+    y_bias: Optional[torch.Tensor] = None
+
+
+@dataclass
 class ResidualSink:
     """Handed to the last product of a sub-layer that may fold the residual add and the norm that
     follows: the residual stream ``x`` and that norm's weight and eps."""

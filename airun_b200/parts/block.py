@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..weights.loader import WeightSpec
-from .base import CastActivations, FeedForward, Mixer, Norm, NormedActivations, Part, ResidualSink, register_part
+from .base import CastActivations, FeedForward, Mixer, Norm, NormedActivations, Part, ResidualSink, StreamWrite, register_part
 
 
 class PreNormBlock(Part):
@@ -346,3 +346,104 @@ class GatedParallelBlock(Part):
 
 
 register_part("arrangement", "gated_parallel", GatedParallelBlock)
+
+
+class HyperConnectionBlock(Part):
+    """A residual of several streams x_1..x_S (hyper-connections).  Each sub-layer f (the mixer, then the feed-forward)
+    has numbers of its own, a[S], M[S, S] (indexed [from, to]) and b[S]:
+
+        u = sum_s a[s] x_s,    y = f(norm(u)),    x_t <- sum_s M[s, t] x_s + m * b[t] * y     (all t from the old streams)
+
+    with m (``residual_mult``) one number of the model.  The streams are all equal to the embedding at the start and
+    are summed at the end (engine/model.py).  Tensors: ``<prefix>.hc1.{in,mix,out}`` for the mixer and ``.hc2.*`` for
+    the feed-forward; with ``learned`` False there are none and every a, M and b is 1 on one stream: the plain pre-norm
+    residual x += m * f(norm(x)).  The write of a sub-layer's result and the read and norm for the next one are ONE
+    pass over the streams (csrc/streams.cu); the last write of the block is left pending for whoever reads the streams
+    next (``StreamWrite``).  A mixer with an ``output_bias`` leaves it to that pass too.  The norms must offer
+    ``fusable()`` (weight, eps) of a root-mean-square norm."""
+    multi_stream = True
+    norm2_belongs_to_ffn = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], dtype: torch.dtype,
+                 prefix: str, streams: int = 1, residual_mult: float = 1.0, learned: bool = True,
+                 names: Optional[Dict[str, str]] = None):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.dtype = norm1, mixer, norm2, ffn, dtype
+        self.prefix, self.S, self.mult, self.learned = prefix, int(streams), float(residual_mult), bool(learned)
+        if self.S < 1 or (not self.learned and self.S != 1):
+            raise ValueError("at least one stream; without learnt connections exactly one")
+        for n_ in (norm1, norm2):
+            if n_ is not None and not hasattr(n_, "fusable"):
+                raise ValueError("a block over several streams needs root-mean-square norms (parts with fusable())")
+        n = dict(read="hc{k}.in", carry="hc{k}.mix", write="hc{k}.out")
+        n.update(names or {})
+        self.n = n
+        self.read: List[Optional[torch.Tensor]] = [None, None]
+        self.carry: List[Optional[torch.Tensor]] = [None, None]
+        self.write: List[Optional[torch.Tensor]] = [None, None]
+
+    def subs(self):
+        return (self.mixer,) if self.ffn is None else (self.mixer, self.ffn)
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
+
+    def _name(self, which: str, k: int) -> str:
+        return f"{self.prefix}.{self.n[which].format(k=k + 1)}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self.parts() for s in p.weight_specs()]
+        if self.learned:
+            for k in range(len(self.subs())):
+                specs += [WeightSpec(self._name("read", k), (self.S,), storage="float32", init="norm"),
+                          WeightSpec(self._name("write", k), (self.S,), storage="float32", init="norm"),
+                          WeightSpec(self._name("carry", k), (self.S, self.S), storage="float32", init="normal")]
+        return specs
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts():
+            p.load_weights(tensors)
+        for k in range(len(self.subs())):
+            if self.learned:
+                self.read[k], self.write[k] = tensors[self._name("read", k)], tensors[self._name("write", k)]
+                self.carry[k] = tensors[self._name("carry", k)]
+            else:
+                dev = self.norm1.fusable()[0].device
+                self.read[k] = torch.ones(1, dtype=torch.float32, device=dev)
+                self.write[k] = torch.ones(1, dtype=torch.float32, device=dev)
+                self.carry[k] = torch.ones(1, 1, dtype=torch.float32, device=dev)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def device_driven(self) -> bool:
+        return all(getattr(p, "device_driven", False) for p in self.parts())
+
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def accepts_normed(self) -> bool:
+        return False
+
+    def forward(self, ctx, xs: torch.Tensor, pending, cache, next_norm: Optional[Norm] = None):
+        """``xs`` float32 [T, S, H]; ``pending``: None or the StreamWrite the block before left."""
+        from ..kernels import ops
+        T, S, H = xs.shape
+        if pending is not None and not isinstance(pending, StreamWrite):
+            raise TypeError("a block over several streams can only follow one of its kind")
+        for k, (sub, norm) in enumerate(zip(self.subs(), (self.norm1, self.norm2))):
+            w, eps = norm.fusable()
+            h = ctx.ws.alloc((T, H), self.dtype)
+            p = pending
+            ops.stream_step(xs, y=p.y if p else None, carry=p.carry if p else None, write=p.write if p else None,
+                            mult=p.mult if p else 1.0, y_bias=p.y_bias if p else None, read=self.read[k], norm_w=w, eps=eps,
+                            out=h, req_of_token=ctx.req_of_token)
+            if k == 0:
+                bias = getattr(sub, "output_bias", None)
+                y = sub.forward(ctx, h, cache, add_bias=False) if bias is not None else sub.forward(ctx, h, cache)
+            else:
+                bias, y = None, sub.forward(ctx, h)
+            pending = StreamWrite(y, self.carry[k], self.write[k], self.mult, bias)
+        return pending
+
+
+register_part("arrangement", "hyper_connections", HyperConnectionBlock)
