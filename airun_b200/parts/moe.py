@@ -45,7 +45,7 @@ class RoutedExperts(FeedForward):
                  dtype: torch.dtype = torch.bfloat16, device=None, names: Optional[Dict[str, str]] = None):
         self.prefix, self.H, self.I = prefix, int(hidden_size), int(intermediate_size)
         self.E, self.top = int(num_experts), int(top)
-        if not (1 <= self.top <= self.E <= 1024):
+        if not (1 <= self.E <= 1024 and 1 <= self.top <= self.E + int(identity_experts)):
             raise ValueError(f"1 to 1024 experts and 1 to all of them a token, found {num_experts} and {top}")
         if scores not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
             raise ValueError("scores is 'sigmoid' or 'softmax', weight_on is 'input' or 'output'")

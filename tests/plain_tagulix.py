@@ -136,12 +136,13 @@ def plain_window_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: 
         k = plain_rotate_pairs(k, pos, rot["dims"], rot["base"])
     q, k = plain_rms(q, eps), plain_rms(k, eps)
     window = (m.get("mask") or {}).get("size", 0)
-    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], window, rnd=rnd)
+    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], window)
     return _r(rnd, o) @ W[p + ".o"].T + W[p + ".o.b"]
 
 
-def plain_bias_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, rnd: Rounding = None):
-    """The left half of the mixer "parallel"."""
+def plain_bias_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, rnd: Rounding = None, out_scale: float = 1.0):
+    """The left half of the mixer "parallel", times ``out_scale`` (applied to the heads' results, where the engine
+    rounds them)."""
     T = h.shape[0]
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
@@ -156,9 +157,8 @@ def plain_bias_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: fl
     bucket = torch.tensor([[plain_distance_bucket(i - j, rows, m["bias_max"]) if j <= i else 0 for j in range(T)]
                            for i in range(T)])
     bias = rel[bucket].permute(2, 0, 1)                       # [heads, T, T]
-    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], 0, bias=bias, sink=W[p + ".sink"],
-                                rnd=rnd)
-    return _r(rnd, o) @ W[p + ".o"].T
+    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], 0, bias=bias, sink=W[p + ".sink"])
+    return _r(rnd, out_scale * o) @ W[p + ".o"].T
 
 
 # ----------------------------------------------------------------------------- linear attention with a fixed decay
@@ -175,21 +175,22 @@ def plain_decay_recurrence(q, k, v, decay: List[float], state: Optional[torch.Te
     return o, S
 
 
-def plain_decay_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, rnd: Rounding = None):
-    """The right half of the mixer "parallel"."""
+def plain_decay_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, rnd: Rounding = None, out_scale: float = 1.0):
+    """The right half of the mixer "parallel", times ``out_scale``.  The engine keeps q, k and v of the recurrence in
+    float32, so nothing is rounded before the gated, normed heads."""
     T = h.shape[0]
     H, D, Dv = m["heads"], m["dim"], m["vdim"]
-    q = _r(rnd, plain_silu(h @ W[p + ".q"].T)).view(T, H, D)
-    k = _r(rnd, plain_silu(h @ W[p + ".k"].T)).view(T, H, D)
-    v = _r(rnd, plain_silu(h @ W[p + ".v"].T)).view(T, H, Dv)
+    q = plain_silu(h @ W[p + ".q"].T).view(T, H, D)
+    k = plain_silu(h @ W[p + ".k"].T).view(T, H, D)
+    v = plain_silu(h @ W[p + ".v"].T).view(T, H, Dv)
     o, _ = plain_decay_recurrence(q, k, v, m["decay"])
     o = plain_rmsnorm(o.reshape(T, H * Dv), W[p + ".norm"], eps) * torch.sigmoid(h @ W[p + ".g"].T)
-    return _r(rnd, o) @ W[p + ".o"].T
+    return _r(rnd, out_scale * o) @ W[p + ".o"].T
 
 
 def plain_parallel_mixer(h, W, p: str, m: dict, eps: float, rnd: Rounding = None):
-    return m["left_scale"] * plain_bias_attention(h, W, p + ".left", m["left"], eps, rnd) \
-        + m["right_scale"] * plain_decay_attention(h, W, p + ".right", m["right"], eps, rnd)
+    return plain_bias_attention(h, W, p + ".left", m["left"], eps, rnd, m["left_scale"]) \
+        + plain_decay_attention(h, W, p + ".right", m["right"], eps, rnd, m["right_scale"])
 
 
 # ----------------------------------------------------------------------------- routed experts
@@ -268,3 +269,145 @@ def plain_forward(config: dict, W: Dict[str, torch.Tensor], tokens: List[int], r
         after.append(xs.sum(dim=0))
     h = _r(rnd, plain_rmsnorm(xs.sum(dim=0), W["final.norm"], eps))
     return h @ W["head"].T, torch.stack(after)
+
+
+def plain_greedy(config: dict, W, prompt: List[int], n_new: int) -> List[int]:
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(torch.argmax(plain_forward(config, W, toks)[0][-1])))
+    return toks[len(prompt):]
+
+
+# ----------------------------------------------------------------------------- configurations and weights
+def moe(ff: int, experts: int, top: int, identity: int = 0, scale: float = 1.0, groups=(1, 1)) -> dict:
+    return dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top, identity=identity, scale=scale,
+                                                             groups=dict(count=groups[0], keep=groups[1])))
+
+
+def attention_layer(heads, kv_heads, dim, vdim, scale=None, window=None, rot=None, mlp=None, weights_of=None) -> dict:
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale if scale is not None else 3.0 * dim ** -0.5)
+    if window:
+        m["mask"] = dict(size=window)
+    if rot:
+        m["rot"] = dict(dims=rot[0], base=rot[1])
+    out = dict(type="attention", mixer=m, mlp=mlp)
+    if weights_of is not None:
+        out["weights_of"] = weights_of
+    return out
+
+
+def parallel_layer(heads, kv_heads, dim, vdim, bias_max, lin_heads, lin_dim, lin_vdim, decay, scale=None, temp=None,
+                   left_scale=1.0, right_scale=1.0, mlp=None, weights_of=None) -> dict:
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale if scale is not None else 1.5 * dim ** -0.5,
+                bias_max=bias_max)
+    if temp:
+        left["q_temp"] = dict(coef=temp[0], every=temp[1])
+    right = dict(heads=lin_heads, dim=lin_dim, vdim=lin_vdim, decay=list(decay))
+    out = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=left_scale, right_scale=right_scale), mlp=mlp)
+    if weights_of is not None:
+        out["weights_of"] = weights_of
+    return out
+
+
+def make_config(vocab, width, layers, eps=1e-5, mult=1.0, streams=None) -> dict:
+    import json
+    d = dict(architecture="Tagulix", vocab=vocab, width=width, norm=dict(eps=eps), residual_mult=mult, layers=layers)
+    if streams is not None:
+        d["streams"] = streams
+    return json.loads(json.dumps(d))
+
+
+def all_experts(config: dict) -> dict:
+    """The same model with every router choosing ALL its outputs (every group kept; the weights still come from the
+    scores): a choice that no rounding can change, for comparisons in reduced precision."""
+    import json
+    out = json.loads(json.dumps(config))
+    for l in out["layers"]:
+        if l.get("mlp"):
+            r = l["mlp"]["router"]
+            r["top"] = r["experts"] + r.get("identity", 0)
+            r["groups"]["keep"] = r["groups"]["count"]
+    return out
+
+
+def tensor_shapes(config: dict, rel_rows: int = 8) -> Dict[str, tuple]:
+    Wd, S, shapes = config["width"], config.get("streams"), {}
+    shapes["embed"] = (config["vocab"], Wd)
+    shapes["head"] = (config["vocab"], Wd)
+    shapes["final.norm"] = (Wd,)
+    for i, l in enumerate(config["layers"]):
+        if "weights_of" in l:
+            continue
+        p, m = f"l{i}", l["mixer"]
+        x = p + ".mix."
+        shapes[p + ".norm1"] = (Wd,)
+        if l["type"] == "attention":
+            H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            shapes.update({x + "q": (H * D, Wd), x + "q.b": (H * D,), x + "k": (G * D, Wd), x + "k.b": (G * D,),
+                           x + "v": (G * Dv, Wd), x + "v.b": (G * Dv,), x + "o": (Wd, H * Dv), x + "o.b": (Wd,)})
+        else:
+            a, r = m["left"], m["right"]
+            H, G, D, Dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            shapes.update({x + "left.q": (H * D, Wd), x + "left.k": (G * D, Wd), x + "left.v": (G * Dv, Wd), x + "left.o": (Wd, H * Dv),
+                           x + "left.q.norm": (D,), x + "left.k.norm": (D,), x + "left.rel": (rel_rows, H), x + "left.sink": (H,)})
+            H, D, Dv = r["heads"], r["dim"], r["vdim"]
+            shapes.update({x + "right.q": (H * D, Wd), x + "right.k": (H * D, Wd), x + "right.v": (H * Dv, Wd),
+                           x + "right.g": (H * Dv, Wd), x + "right.o": (Wd, H * Dv), x + "right.norm": (H * Dv,)})
+        subs = [1]
+        mlp = l.get("mlp")
+        if mlp:
+            subs.append(2)
+            r, ff = mlp["router"], mlp["expert"]["ff"]
+            shapes.update({p + ".norm2": (Wd,), p + ".mlp.router": (r["experts"] + r["identity"], Wd),
+                           p + ".mlp.correction": (r["experts"] + r["identity"],)})
+            for e in range(r["experts"]):
+                shapes.update({f"{p}.mlp.e{e}.up": (ff, Wd), f"{p}.mlp.e{e}.down": (Wd, ff)})
+        if S:
+            for q in subs:
+                shapes.update({f"{p}.hc{q}.in": (S,), f"{p}.hc{q}.out": (S,), f"{p}.hc{q}.mix": (S, S)})
+    return shapes
+
+
+def random_weights(config: dict, seed: int, gain: float = 1.0, rel_rows: int = 8) -> Dict[str, torch.Tensor]:
+    """Weights large enough that every mechanism moves the logits: matrices N(0, gain^2 / fan_in), norm weights near 1
+    (the q/k norms larger, so that the attention is peaked), distance biases and sinks of a visible size, connections
+    between the streams near a rotation of them; all rounded to bfloat16, the file's type."""
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    for name, shape in tensor_shapes(config, rel_rows).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf == "mix":
+            S = shape[0]
+            t = 0.6 * torch.eye(S) + 0.4 * torch.roll(torch.eye(S), 1, 1) + 0.1 * torch.randn(shape, generator=g)
+        elif leaf in ("in", "out"):
+            t = 1.0 / shape[0] ** 0.5 + 0.3 * torch.randn(shape, generator=g)
+        elif leaf == "rel":
+            t = 1.5 * torch.randn(shape, generator=g)
+        elif leaf == "sink":
+            t = 1.0 + torch.randn(shape, generator=g)
+        elif leaf == "correction":
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif name.endswith("q.norm") or name.endswith("k.norm"):
+            t = 1.6 + 0.3 * torch.randn(shape, generator=g)
+        elif len(shape) == 2:
+            std = 1.0 if name == "embed" else gain / math.sqrt(shape[1])
+            if leaf == "router":
+                std *= 2.0
+            t = torch.randn(shape, generator=g) * std
+        elif leaf == "b":
+            t = 0.3 * torch.randn(shape, generator=g)
+        else:                                               # norm weights
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        W[name] = t.to(torch.bfloat16)
+    return W
+
+
+def write_folder(folder: str, config: dict, W: Dict[str, torch.Tensor]) -> str:
+    import json
+    import os
+    from safetensors.torch import save_file
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config, f)
+    save_file({n: t.contiguous() for n, t in W.items()}, os.path.join(folder, "model.safetensors"))
+    return folder
