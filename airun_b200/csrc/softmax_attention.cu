@@ -17,7 +17,7 @@
 #include "common.cuh"
 
 #define XA_MAX_PER_LANE 8     // D <= 256 and Dv <= 256
-#define XA_PREP_WARPS 4
+#define XA_PREP_WARPS 8
 #define XA_WARPS 4
 
 #define XA_ROPE_NONE 0
@@ -61,6 +61,11 @@ __global__ __launch_bounds__(32 * XA_PREP_WARPS) void qkv_prepare_kernel(
     }
     const float* row = proj + (size_t)t * proj_stride;
     const float rpos = (float)(rope_positions ? rope_positions[t] : pos);
+    // the angles are the same for every head of the token: one sine and cosine per rotated pair, worked out once
+    __shared__ float s_cos[16 * XA_MAX_PER_LANE], s_sin[16 * XA_MAX_PER_LANE];
+    if (rope_kind != XA_ROPE_NONE)
+        for (int i = threadIdx.x; i < (rdim >> 1); i += blockDim.x) sincosf(rpos * inv_freq[i], &s_sin[i], &s_cos[i]);
+    __syncthreads();
     const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
     const int units = nh + (store ? nkv : 0);
     float* sx = s_x[warp];
@@ -98,8 +103,7 @@ __global__ __launch_bounds__(32 * XA_PREP_WARPS) void qkv_prepare_kernel(
                 bool first;
                 if (rope_kind == XA_ROPE_INTERLEAVED) { pair = d >> 1; first = (d & 1) == 0; other = d ^ 1; }
                 else { first = d < half; pair = first ? d : d - half; other = first ? d + half : d - half; }
-                float sn, cs;
-                sincosf(rpos * inv_freq[pair], &sn, &cs);
+                const float sn = s_sin[pair], cs = s_cos[pair];
                 const float o = sx[other];
                 x[i] = first ? x[i] * cs - o * sn : x[i] * cs + o * sn;
             }

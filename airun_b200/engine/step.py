@@ -296,8 +296,18 @@ class StepRunner:
             torch.cuda.current_stream().synchronize()
             before = ops.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = self.model.forward(ctx, want_rows, n_want)
+            # no garbage collection while the stream is capturing: a collected engine or graph of an earlier run frees
+            # device memory and graphs, which is not allowed then and ends the capture with an error
+            import gc
+            gc.collect()
+            was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    out = self.model.forward(ctx, want_rows, n_want)
+            finally:
+                if was_on:
+                    gc.enable()
             entry = (graph, out, ops.LAUNCHES[0] - before)
             ops.LAUNCHES[0] = before
             self.graphs[key] = entry

@@ -760,3 +760,57 @@ def sigmoid_attention_bf16(ctx, q, out, cache, part) -> bool:
     f = _fn("sigmoid_attention_mma", "airun_sigmoid_attention_mma", sig + [c_int] + csig + [c_int, c_void_p, c_void_p])
     _check(f(*common, max_tiles, *consts, 1 if single else 0, _p(ctx.err), _stream()), "sigmoid_attention_mma")
     return True
+
+
+def softmax_attention_bf16(ctx, q, out, cache, part) -> bool:
+    """Softmax attention with a window, a distance table, a sink and a factor on the tensor cores
+    (csrc/softmax_attention_mma.cu) for every row of the batch: prompt portions in tiles of 64 tokens of one head, single
+    tokens with the query heads of a KV head as the rows and their keys cut into slices; False: the caller runs the
+    plain kernel (head sizes above 128)."""
+    D, Dv, nh, nkv = part.D, part.Dv, part.nh, part.nkv
+    if ("softmax_attention" in DISABLED or q.dtype != torch.bfloat16 or cache.pool.dtype != torch.bfloat16 or D > 128 or Dv > 128
+            or q.data_ptr() % 16 or cache.pool.data_ptr() % 16):
+        return False
+    _cuda(q, out, cache.pool, cache.block_table, ctx.cu_tokens, ctx.context_lens, ctx.err, part.table, part.sink)
+    T = q.shape[0]
+    _need(tuple(q.shape) == (T, nh * D) and q.is_contiguous(), "q must be contiguous [T, heads*D]")
+    _need(tuple(out.shape) == (T, nh * Dv) and out.stride(1) == 1 and out.dtype == torch.bfloat16,
+          "out must be row-major bfloat16 [T, heads*Dv]")
+    pool, bt = cache.pool, cache.block_table
+    _need(pool.is_contiguous() and pool[0].numel() == nkv * cache.page_size * (D + Dv), "the cache pages do not fit the head sizes")
+    _need(ctx.cu_tokens.numel() >= ctx.num_reqs + 1 and ctx.context_lens.numel() >= ctx.num_reqs,
+          "the batch's layout arrays are shorter than its number of requests")
+    table_len = 0
+    if part.table is not None:
+        _need(part.table.dtype == torch.float32 and part.table.dim() == 2 and part.table.shape[0] == nh and part.table.is_contiguous(),
+              "the distance table must be float32 [heads, n]")
+        table_len = part.table.shape[1]
+    _need(part.sink is None or (part.sink.dtype == torch.float32 and part.sink.numel() == nh and part.sink.is_contiguous()),
+          "the sinks must be float32 [heads]")
+    common = [_p(q), _p(out), out.stride(0) if T > 1 else max(out.shape[1], out.stride(0)), _p(pool), _p(bt), bt.stride(0),
+              _p(ctx.cu_tokens), _p(ctx.context_lens), int(ctx.num_reqs)]
+    consts = [pool.shape[0], int(cache.page_size), nh, nkv, D, Dv, float(part.scale), _p(part.table), int(table_len), _p(part.sink),
+              int(part.window), float(part.out_scale)]
+    sig = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int]
+    csig = [c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_float]
+    # requests that bring ONE token go to the kernel whose product rows are the query heads of a KV head (groups of up
+    # to 16), which finds them on the device; the tile kernel then skips them
+    single = "softmax_group" not in DISABLED and nh // nkv <= 16
+    decode_only = bool(getattr(ctx, "decode_only", False))
+    lens = None if ctx.extras.get("device_plan") else getattr(ctx, "query_lens", None)
+    if single and (decode_only or lens is None or 1 in list(lens)):
+        context = ctx.extras.get("planning_context_len", ctx.max_context_len)
+        if part.window > 0:
+            context = min(context, part.window)
+        splits = plan_sigmoid_slices(int(ctx.num_reqs), nkv, int(context), sigmoid_group_resident(D, Dv) * machine(q.device).sms)
+        partial = ctx.ws.alloc((splits, T, nh * (Dv + 2)), torch.float32) if splits > 1 else None
+        f = _fn("softmax_attention_mma", "airun_softmax_attention_group", sig + csig + [c_int, c_void_p, c_int, c_void_p, c_void_p])
+        _check(f(*common, *consts, splits, _p(partial), T, _p(ctx.err), _stream()), "softmax_attention_group")
+    if single and decode_only:
+        return True
+    # every other request's tokens are cut into tiles of 64; the kernel walks cu_tokens to find its tile, so the
+    # launch only needs an upper bound of their number
+    max_tiles = (T + SIGMOID_TILE_ROWS - 1) // SIGMOID_TILE_ROWS + int(ctx.num_reqs)
+    f = _fn("softmax_attention_mma", "airun_softmax_attention_mma", sig + [c_int] + csig + [c_int, c_void_p, c_void_p])
+    _check(f(*common, max_tiles, *consts, 1 if single else 0, _p(ctx.err), _stream()), "softmax_attention_mma")
+    return True

@@ -143,7 +143,7 @@ class SoftmaxAttention(Mixer):
     def attend(self, ctx, q: torch.Tensor, out: torch.Tensor, cache) -> None:
         if q.dtype == torch.bfloat16:
             from ..kernels import fast
-            if hasattr(fast, "softmax_attention_bf16") and fast.softmax_attention_bf16(ctx, q, out, cache, self):
+            if fast.softmax_attention_bf16(ctx, q, out, cache, self):
                 return
         ops.softmax_attention(q, out, cache, ctx, self.nh, self.nkv, self.D, self.Dv, self.scale, self.table, self.sink,
                               self.window, self.out_scale)

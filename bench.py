@@ -1015,6 +1015,154 @@ def workload_gamanex(a) -> int:
     return 0
 
 
+# The Tagulix design beside the dense Qwen3 decoder at equal size (--workload tagulix)
+def tagulix_pair(size: dict):
+    """(Tagulix configuration, Qwen3 configuration) with the same width, head counts (heads of 128), vocabulary and six
+    layer runs.  Tagulix: four residual streams; a windowed softmax attention (window 1,024, half of each head rotated)
+    and a pair of mixers side by side (causal softmax attention with a distance table, a sink and a query temperature,
+    beside a decayed linear attention of half as many heads, 64 x 128) in turn; the third and fifth run use the first
+    layer's tensors and the sixth the second's; every layer routes a token to 4 of 16 + 2 experts (two groups of which
+    one is kept) of a quarter of the dense feed-forward size, without a gate: 2 W F multiply-adds where Qwen3 has 3."""
+    from airun_b200.config import TagulixConfig
+    W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+    moe = dict(kind="moe", expert=dict(ff=F // 4), router=dict(experts=16, top=4, identity=2, scale=2.0, groups=dict(count=2, keep=1)))
+    att = dict(type="attention", mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=0.1, mask=dict(size=1024),
+                                            rot=dict(dims=64, base=10000.0)), mlp=moe)
+    par = dict(type="parallel", mixer=dict(
+        left=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, bias_max=2048, q_temp=dict(coef=0.3, every=512)),
+        right=dict(heads=H // 2, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(3 + i % 6) for i in range(H // 2)]),
+        left_scale=1.0, right_scale=1.0), mlp=moe)
+    layers = [att, par, dict(att, weights_of=0), par, dict(att, weights_of=0), dict(par, weights_of=1)]
+    tag = TagulixConfig.from_dict(dict(architecture="Tagulix", vocab=VEDIZEN_VOCAB, width=W, norm=dict(eps=1e-5), residual_mult=0.5,
+                                       streams=4, layers=layers))
+    return tag, vedizen_pair(size)[1]
+
+
+def workload_tagulix(a) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 and 64 at a context of 1,024) of the Tagulix design and of
+    the Qwen3 decoder at equal size, through the step function and its CUDA graphs, and how long each kind of kernel
+    runs inside the prefill step and the batch-64 decode step (CUDA events around every call of the kind, the step
+    launched kernel by kernel), with the fraction of the measured peak its bytes or FLOPs over that time come to.  One
+    JSON line per size."""
+    import torch
+    from airun_b200 import Engine, EngineOptions, StepEntry
+    from airun_b200.kernels import fast, ops
+    pk = peaks()
+    T, ctx_len, steps = 2048, 1024, max(8, min(a.steps, 32))
+    for name in (a.sizes.split(",") if a.sizes else list(VEDIZEN_SIZES)):
+        size = VEDIZEN_SIZES[name]
+        W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+        line = {"workload": "tagulix", "size": size, "layer_runs": 6, "vocab": VEDIZEN_VOCAB, "dtype": "bf16",
+                "data": "synthetic, random weights", "prompt": T, "decode_context": ctx_len, "peaks": pk["source"], "models": {}}
+        for model, cfg in zip(("tagulix", "qwen3"), tagulix_pair(size)):
+            eng = Engine.from_config(cfg, seed=0, options=EngineOptions(
+                dtype="bfloat16", page_size=16, cache_tokens=64 * (ctx_len + 4 * steps + 64) + 4096, max_batch_tokens=T,
+                max_requests=64, max_context=max(T, ctx_len + 4 * steps + 64)))
+            tri = lambda t: t * (t + 1) / 2                                   # keys all tokens of a t-token prompt see together
+            win = lambda t: tri(min(t, 1024)) + max(0, t - 1024) * 1024.0     # the same under a window of 1,024
+            # kind -> (module, function, work at t tokens of one prompt, work at a batch of b single tokens, bound)
+            if model == "tagulix":
+                S, Fe, E, top, Hl = 4, F // 4, 16, 4, H // 2
+                lin_in, lin_out = Hl * (64 * 2 + 128 * 2) * 4.0, Hl * 128 * 4.0
+                kinds = {
+                    "streams: write, read and norm in one pass": (ops, "stream_step", lambda t: 13 * t * W * (8.0 * S + 6), lambda b: 13 * b * W * (8.0 * S + 6), "hbm"),
+                    "q/k norm, rotation, temperature, cache write": (ops, "qkv_prepare", lambda t: 6 * t * (H + 2 * G) * 128 * 6.0,
+                                                                     lambda b: 6 * b * (H + 2 * G) * 128 * 6.0, "hbm"),
+                    "softmax attention (window; table and sink)": (fast, "softmax_attention_bf16", lambda t: 3 * H * 4.0 * 128 * (tri(t) + win(t)),
+                                                                   lambda b: 6 * b * ctx_len * G * 256 * 2.0, "mixed"),
+                    "decayed linear attention: recurrence": (ops, "decay_recurrent", lambda t: 3 * t * (lin_in - Hl * 128 * 4.0 + lin_out),
+                                                             lambda b: 3 * b * (Hl * 64 * 128 * 8.0), "hbm"),
+                    "norm over all heads and gate": (ops, "rownorm_gate", lambda t: 3 * t * Hl * 128 * 10.0, lambda b: 3 * b * Hl * 128 * 10.0, "hbm"),
+                    "expert products (up + GELU, down)": (fast, "grouped_linear_bf16", lambda t: 6 * t * top * 4.0 * W * Fe,
+                                                          lambda b: 6 * min(E, b * top) * 2 * W * Fe * 2.0, "tensor"),
+                    "router with groups": (ops, "moe_route_grouped", lambda t: 6 * t * (E + 2 + 3 * top) * 4.0, lambda b: 6 * b * (E + 2 + 3 * top) * 4.0, "hbm"),
+                    "rows to experts and back": (ops, "moe_scatter", lambda t: 6 * t * (W * 2 + top * W * 2.0), lambda b: 6 * b * (W * 2 + top * W * 2.0), "hbm"),
+                    "sum of a token's experts": (ops, "moe_combine", lambda t: 6 * t * (top + 1) * W * 4.0, lambda b: 6 * b * (top + 1) * W * 4.0, "hbm"),
+                }
+            else:
+                kinds = {
+                    "norm (rms)": (ops, "rmsnorm", lambda t: 13 * t * W * 14.0, lambda b: 13 * b * W * 14.0, "hbm"),
+                    "q/k norm + rotary + cache write": (ops, "qkv_post", lambda t: 6 * t * (H + 2 * G) * 128 * 6.0,
+                                                        lambda b: 6 * b * (H + 2 * G) * 128 * 6.0, "hbm"),
+                    "attention": (fast, "attention_bf16", lambda t: 6 * H * 4.0 * 128 * tri(t), lambda b: 6 * b * ctx_len * G * 256 * 2.0, "mixed"),
+                    "gate/up product + gated unit": (fast, "linear_swiglu_bf16", lambda t: 6 * 2.0 * t * W * 2 * F, lambda b: 6 * W * 2 * F * 2.0, "tensor"),
+                }
+            kinds = {k: v for k, v in kinds.items() if hasattr(v[0], v[1])}
+            res = {}
+            pre_ms = time_prefill(eng, T, runs=5)
+            b64 = time_decode_onward(eng, 64, ctx_len, steps, a.warmup, "v")
+            b8 = time_decode_onward(eng, 8, ctx_len, steps, a.warmup, "w")
+            res["prefill"] = {"ms": round(pre_ms, 3), "tokens_per_s": round(T / pre_ms * 1e3, 1)}
+            res["decode_b8"] = {"ms_per_step": round(b8, 4), "tokens_per_s": round(8 / b8 * 1e3, 1)}
+            res["decode_b64"] = {"ms_per_step": round(b64, 4), "tokens_per_s": round(64 / b64 * 1e3, 1)}
+            spans = {k: [] for k in kinds}
+            real = {k: getattr(v[0], v[1]) for k, v in kinds.items()}
+
+            def timed(kind):
+                def call(*x, **kw):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    out = real[kind](*x, **kw)
+                    e1.record()
+                    spans[kind].append((e0, e1))
+                    return out
+                return call
+
+            def step_times(run):
+                best = {}
+                for _ in range(4):
+                    for k in spans:
+                        spans[k].clear()
+                    run()
+                    torch.cuda.synchronize()
+                    for k, evs in spans.items():
+                        us = sum(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
+                        best[k] = min(best.get(k, us), us)
+                return best
+
+            toks = torch.randint(0, eng.config.vocab_size, (T,), generator=torch.Generator().manual_seed(3)).tolist()
+            rids = [f"k{i}" for i in range(64)]
+            count = [0]
+
+            def run_prefill():
+                count[0] += 1
+                eng.manager.add_request(f"kp{count[0]}")
+                eng.runner.step([StepEntry(f"kp{count[0]}", toks, (T - 1,))])
+                eng.manager.free_request(f"kp{count[0]}")
+
+            def run_decode():
+                eng.runner.step([StepEntry(r, [toks[j]], (0,)) for j, r in enumerate(rids)])
+
+            graphs, eng.runner.use_graphs = eng.runner.use_graphs, False
+            for k, v in kinds.items():
+                setattr(v[0], v[1], timed(k))
+            try:
+                pre_t = step_times(run_prefill)
+                fill_contexts(eng, rids, ctx_len)
+                dec_t = step_times(run_decode)
+            finally:
+                for k, v in kinds.items():
+                    setattr(v[0], v[1], real[k])
+                eng.runner.use_graphs = graphs
+            for r in rids:
+                eng.manager.free_request(r)
+            res["kernels"] = {}
+            for kind, (_, _, work_p, work_d, bound) in kinds.items():
+                pre_us, dec_us = max(pre_t[kind], 1e-3), max(dec_t[kind], 1e-3)
+                row = {"prefill_us": round(pre_us, 1), "decode_b64_us": round(dec_us, 1)}
+                if bound == "hbm":
+                    row["prefill_frac_of_hbm"] = round(work_p(T) / pre_us / 1e3 / pk["hbm_gbs"], 4)
+                else:
+                    row["prefill_frac_of_bf16_peak"] = round(work_p(T) / pre_us * 1e6 / (pk["bf16_tflops"] * 1e12), 4)
+                row["decode_b64_frac_of_hbm"] = round(work_d(64) / dec_us / 1e3 / pk["hbm_gbs"], 4)
+                res["kernels"][kind] = row
+            line["models"][model] = res
+            del eng
+            torch.cuda.empty_cache()
+        print(json.dumps(line), flush=True)
+    return 0
+
+
 def reference_arm(a) -> int:
     """The same metric on the reference's own CUDA kernels (compiled unmodified for sm_100), called
     through their C entry points in the order the reference's runtime calls them
@@ -1194,14 +1342,15 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling runs)")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prompt only (for profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate", "vedizen", "pogarax", "gamanex"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "serve", "long", "ablate", "vedizen", "pogarax", "gamanex", "tagulix"),
                     help="decode: the headline line; serve: 128 requests continuously batched (Qwen3-1.7B shape); "
                          "long: a 32,768-token prompt, then decoding alone and as 16 forks (Qwen3-32B shape); "
                          "ablate: the decode step timed with one kind of kernel left out at a time; "
                          "vedizen: prefill and decode of the Vedizen design beside the Qwen3 decoder at equal size; "
                          "pogarax: the same for the Pogarax design beside the Vedizen design; "
-                         "gamanex: the same for the Gamanex design beside the Qwen3 decoder")
-    ap.add_argument("--sizes", default="", help="vedizen / pogarax / gamanex: widths to run, comma separated (default: 2048,4096)")
+                         "gamanex: the same for the Gamanex design beside the Qwen3 decoder; "
+                         "tagulix: the same for the Tagulix design beside the Qwen3 decoder")
+    ap.add_argument("--sizes", default="", help="vedizen / pogarax / gamanex / tagulix: widths to run, comma separated (default: 2048,4096)")
     ap.add_argument("--requests", type=int, default=128, help="serve: requests")
     ap.add_argument("--new-tokens", type=int, default=None, help="serve / long: tokens decoded per request")
     ap.add_argument("--budget", type=int, default=512, help="serve: tokens per step")
@@ -1228,6 +1377,8 @@ def main() -> int:
         return workload_pogarax(a)
     if a.workload == "gamanex":
         return workload_gamanex(a)
+    if a.workload == "tagulix":
+        return workload_tagulix(a)
 
     import torch
     from airun_b200 import Engine, EngineOptions, Qwen3Config

@@ -101,7 +101,8 @@ def plain_softmax_attention(q, k, v, heads: int, kv_heads: int, scale: float, wi
                             bias: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
                             rnd: Rounding = None) -> torch.Tensor:
     """q [T, heads, D], k [T, kv_heads, D], v [T, kv_heads, Dv] -> [T, heads * Dv].  ``bias`` [heads, T, T] is added
-    to the scaled scores; ``sink`` [heads] adds exp(sink_h) to the denominator and nothing to the numerator."""
+    to the scaled scores; ``sink`` [heads] adds exp(sink_h) to the denominator and nothing to the numerator.  ``rnd``
+    rounds the weights where the tensor-core kernel hands them to the second product (it forms them in float32)."""
     T = q.shape[0]
     see = plain_causal(T, window)
     outs = []
@@ -136,7 +137,7 @@ def plain_window_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: 
         k = plain_rotate_pairs(k, pos, rot["dims"], rot["base"])
     q, k = plain_rms(q, eps), plain_rms(k, eps)
     window = (m.get("mask") or {}).get("size", 0)
-    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], window)
+    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], window, rnd=rnd)
     return _r(rnd, o) @ W[p + ".o"].T + W[p + ".o.b"]
 
 
@@ -157,7 +158,7 @@ def plain_bias_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: fl
     bucket = torch.tensor([[plain_distance_bucket(i - j, rows, m["bias_max"]) if j <= i else 0 for j in range(T)]
                            for i in range(T)])
     bias = rel[bucket].permute(2, 0, 1)                       # [heads, T, T]
-    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], 0, bias=bias, sink=W[p + ".sink"])
+    o = plain_softmax_attention(_r(rnd, q), _r(rnd, k), _r(rnd, v), H, G, m["scale"], 0, bias=bias, sink=W[p + ".sink"], rnd=rnd)
     return _r(rnd, out_scale * o) @ W[p + ".o"].T
 
 

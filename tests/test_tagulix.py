@@ -114,7 +114,10 @@ def compare(got, cfg, W, seq, dtype, what):
     if dtype == "float32":
         return assert_close(got, exact.astype(np.float32), dtype, what)
     rounded = P.plain_forward(cfg, W, seq, rnd=P.to_bf16_and_back)[0].numpy()
-    assert_close(got, rounded.astype(np.float32), dtype, what, bf16_noise(rounded, exact))
+    # the engine's rounding is another draw of the same noise (other tile borders, other orders of the sums, weights
+    # rounded against a running maximum), and this design rounds in more places a layer than the others: a row is held
+    # to three times its own noise, where helpers.assert_close alone would hold it to two
+    assert_close(got, rounded.astype(np.float32), dtype, what, 1.5 * bf16_noise(rounded, exact))
 
 
 def pick(folders, name, dtype):
@@ -435,6 +438,66 @@ def test_attention_kernels_over_scrambled_pages(shape, mode, dtype):
     want = plain_case(reqs, consts, spans, live, nh, nkv, D, Dv, scale, mode, rot, temp, window, rel, far, sink, 1.3)
     tol = 2e-5 if dtype == torch.float32 else 4e-2
     assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
+
+
+def run_attention_tc(q, cache, ctx, nh, nkv, D, Dv, scale, rel, far, sink, window, out_scale=1.0):
+    """The tensor-core kernels (tiles for portions, head groups with key slices for single tokens) on the same batch."""
+    from airun_b200.kernels import fast
+    from airun_b200.parts.softmax_attention import distance_buckets
+    table = None
+    if rel is not None:
+        table = dev(rel)[torch.tensor(distance_buckets(rel.shape[0], far), device="cuda")].t().contiguous()
+    part = SimpleNamespace(D=D, Dv=Dv, nh=nh, nkv=nkv, scale=scale, table=table, sink=None if sink is None else dev(sink), window=window,
+                           out_scale=out_scale)
+    wide = torch.zeros(q.shape[0], nh * Dv + 16, device="cuda", dtype=q.dtype)
+    out = wide[:, 8:8 + nh * Dv]
+    assert fast.softmax_attention_bf16(ctx, q, out, cache, part)
+    assert int(ctx.err.item()) == 0 and float(wide[:, :8].abs().max()) == 0 and float(wide[:, 8 + nh * Dv:].abs().max()) == 0
+    return out.float().cpu().double()
+
+
+@gpu
+@pytest.mark.parametrize("shape", [s_ for s_ in ATT_SHAPES if s_[2] <= 128 and s_[3] <= 128])
+@pytest.mark.parametrize("mode", ["unit", "weight"])
+@pytest.mark.parametrize("new", [[13, 23, 1], [1, 1, 1]])
+def test_tensor_core_attention_against_the_plain_kernel_and_the_formula(shape, mode, new):
+    """A portion beside a whole prompt beside a single token, and single tokens alone (700, 23 and 1500 keys: the keys
+    of a single token are cut into slices, and the short request's later slices are empty)."""
+    nh, nkv, D, Dv, page = shape
+    g = torch.Generator().manual_seed(D + nh)
+    unit = mode == "unit"
+    rot = (D // 2 // 2 * 2, 500.0) if unit and D >= 4 else None
+    temp = (0.0, 0) if unit else (0.6, 5)
+    rel, far = (None, 0) if unit else (1.5 * torch.randn(10, nh, generator=g), 37)
+    sink = None if unit else 1.0 + torch.randn(nh, generator=g)
+    window = 90 if unit else 0
+    seqs = [70, 23, 91] if new[0] > 1 else [700, 23, 1500]
+    reqs, consts, cache, (spans, ctx, q, live) = attention_case(seqs, new, nh, nkv, D, Dv, page, torch.bfloat16, 5, mode, rot, temp, bias=unit)
+    scale = (2.0 if unit else 0.8) * D ** -0.5
+    want = plain_case(reqs, consts, spans, live, nh, nkv, D, Dv, scale, mode, rot, temp, window, rel, far, sink, 1.3)
+    got = run_attention_tc(q, cache, ctx, nh, nkv, D, Dv, scale, rel, far, sink, window, out_scale=1.3)
+    plain = run_attention(q, cache, ctx, nh, nkv, D, Dv, scale, rel, far, sink, window, out_scale=1.3)
+    assert torch.allclose(got, want, atol=1e-1, rtol=3e-2), float((got - want).abs().max())       # bfloat16 q, k, v against float64
+    assert torch.allclose(got, plain, atol=3e-2, rtol=3e-2), float((got - plain).abs().max())     # the same inputs: only the weights' rounding
+
+
+@gpu
+@pytest.mark.parametrize("window", [1, 63, 64, 65, 200])
+@pytest.mark.parametrize("new", [1, 70])
+def test_tensor_core_window_edges_key_by_key(window, new):
+    nh = nkv = 1
+    n, D, Dv, page = 300, 8, 128, 8
+
+    def spike(proj, n_):
+        proj[:, :2 * D] = 0.0
+        proj[:, 2 * D:] = torch.eye(n_, n_)[:, -Dv:]           # the last 128 keys spell out their position
+    reqs, consts, cache, (spans, ctx, q, live) = attention_case([n], [new], nh, nkv, D, Dv, page, torch.bfloat16, 1, "weight", spike=spike)
+    got = run_attention_tc(q, cache, ctx, nh, nkv, D, Dv, 1.0, None, 0, None, window)
+    for row, i in enumerate(range(n - new, n)):
+        lo = max(0, i - window + 1)
+        want = torch.zeros(n, dtype=F64)
+        want[lo:i + 1] = 1.0 / (i + 1 - lo)
+        assert torch.allclose(got[row], want[-Dv:], atol=4e-3), (i, window)
 
 
 @gpu
