@@ -37,7 +37,7 @@ def parse_ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="airun", description="airun_b200: inference on one B200 (dense Qwen3, Vedizen, Pogarax and Gamanex decoders)")
+    ap = argparse.ArgumentParser(prog="airun", description="airun_b200: inference on one B200 (dense Qwen3, Vedizen, Pogarax, Gamanex and Tagulix decoders)")
     sub = ap.add_subparsers(dest="cmd", required=True)
 
     run = sub.add_parser("run", help="generate from a prompt of token ids")

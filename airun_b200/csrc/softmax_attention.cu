@@ -24,6 +24,12 @@
 #define XA_ROPE_NEOX 1
 #define XA_ROPE_INTERLEAVED 2
 
+__device__ __forceinline__ void xa_store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void xa_store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
 // One block per token; a warp takes a head at a time (the query heads, then the key heads); then all threads copy
 // the values.  proj is float32 [T][nh*D (+ nkv*D + nkv*Dv when store)], bias the same columns (or null).
 template <typename T>
@@ -69,6 +75,96 @@ __global__ __launch_bounds__(32 * XA_PREP_WARPS) void qkv_prepare_kernel(
     const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
     const int units = nh + (store ? nkv : 0);
     float* sx = s_x[warp];
+    // Head sizes in multiples of four on 16-byte boundaries: a lane takes four neighbouring dimensions (eight for heads
+    // above 128) with one load each, so both dimensions of a rotated pair (2i, 2i + 1) lie in the lane that turns them.
+    const bool vec4 = (D & 3) == 0 && (proj_stride & 3) == 0 && ((uintptr_t)proj & 15) == 0 && (!bias || ((uintptr_t)bias & 15) == 0) &&
+                      ((uintptr_t)q_out & 15) == 0 && (!store || ((uintptr_t)pool & 15) == 0) && rope_kind != XA_ROPE_NEOX &&
+                      (!q_w || ((uintptr_t)q_w & 15) == 0) && (!k_w || ((uintptr_t)k_w & 15) == 0);
+    if (vec4) {
+        for (int u = warp; u < units; u += XA_PREP_WARPS) {
+            const bool is_q = u < nh;
+            const int col0 = u * D;
+            const float* w = is_q ? q_w : k_w;
+            float4 x[2];
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int d = 4 * lane + 128 * i;
+                x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (d < D) {
+                    x[i] = *reinterpret_cast<const float4*>(row + col0 + d);
+                    if (bias) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bias + col0 + d);
+                        x[i].x += b4.x; x[i].y += b4.y; x[i].z += b4.z; x[i].w += b4.w;
+                    }
+                }
+                ss = fmaf(x[i].x, x[i].x, ss); ss = fmaf(x[i].y, x[i].y, ss); ss = fmaf(x[i].z, x[i].z, ss); ss = fmaf(x[i].w, x[i].w, ss);
+            }
+            if (w) {
+                const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int d = 4 * lane + 128 * i;
+                    if (d < D) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(w + d);
+                        x[i].x *= inv * w4.x; x[i].y *= inv * w4.y; x[i].z *= inv * w4.z; x[i].w *= inv * w4.w;
+                    }
+                }
+            }
+            if (rope_kind == XA_ROPE_INTERLEAVED) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int d = 4 * lane + 128 * i;
+                    if (d < rdim && d < D) {
+                        const float c0 = s_cos[d >> 1], s0 = s_sin[d >> 1];
+                        const float a = x[i].x, b = x[i].y;
+                        x[i].x = a * c0 - b * s0; x[i].y = b * c0 + a * s0;
+                    }
+                    if (d + 2 < rdim && d < D) {
+                        const float c1 = s_cos[(d >> 1) + 1], s1 = s_sin[(d >> 1) + 1];
+                        const float a = x[i].z, b = x[i].w;
+                        x[i].z = a * c1 - b * s1; x[i].w = b * c1 + a * s1;
+                    }
+                }
+            }
+            float mulv = is_q ? temp : 1.0f;
+            if (unit_norm) {
+                float s2 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    s2 = fmaf(x[i].x, x[i].x, s2); s2 = fmaf(x[i].y, x[i].y, s2); s2 = fmaf(x[i].z, x[i].z, s2); s2 = fmaf(x[i].w, x[i].w, s2);
+                }
+                const float inv = 1.0f / sqrtf(warp_sum(s2) / (float)D + eps);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) { x[i].x *= inv; x[i].y *= inv; x[i].z *= inv; x[i].w *= inv; }
+            }
+            T* dst = is_q ? q_out + ((size_t)t * nh + u) * D : pk + ((size_t)(u - nh) * page_size + slot) * D;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int d = 4 * lane + 128 * i;
+                if (d < D) xa_store4(dst + d, make_float4(x[i].x * mulv, x[i].y * mulv, x[i].z * mulv, x[i].w * mulv));
+            }
+        }
+        if (!store) return;
+        const int vcol = (nh + nkv) * D;
+        if ((Dv & 3) == 0) {
+            for (int c = threadIdx.x; c < (nkv * Dv) >> 2; c += blockDim.x) {
+                const int g = (4 * c) / Dv, e = 4 * c - g * Dv;
+                float4 v4 = *reinterpret_cast<const float4*>(row + vcol + 4 * c);
+                if (bias) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bias + vcol + 4 * c);
+                    v4.x += b4.x; v4.y += b4.y; v4.z += b4.z; v4.w += b4.w;
+                }
+                xa_store4(pv + ((size_t)g * page_size + slot) * Dv + e, v4);
+            }
+            return;
+        }
+        for (int c = threadIdx.x; c < nkv * Dv; c += blockDim.x) {
+            const int g = c / Dv, e = c - g * Dv;
+            pv[((size_t)g * page_size + slot) * Dv + e] = from_f32<T>(row[vcol + c] + (bias ? bias[vcol + c] : 0.0f));
+        }
+        return;
+    }
     for (int u = warp; u < units; u += XA_PREP_WARPS) {
         const bool is_q = u < nh;
         const int col0 = u * D;                      // q heads and k heads follow each other in the row

@@ -534,6 +534,53 @@ def check_gemm_tc_activation(dev) -> Tuple[float, float]:
     return worst, 2.0 ** -7
 
 
+def check_streams(dev) -> Tuple[float, float]:
+    """A residual of several streams: x_t <- sum_s M[s, t] x_s + m b[t] (y + bias), then u = sum_s a[s] x_s and its norm."""
+    from .kernels import ops
+    worst = 0.0
+    for T, S, H in ((7, 3, 100), (40, 4, 1024)):
+        xs, y, yb = torch.randn(T, S, H), torch.randn(T, H), torch.randn(H)
+        M, b, a, w = torch.randn(S, S), torch.randn(S), torch.randn(S), 1 + 0.3 * torch.randn(H)
+        xd, out = xs.to(dev), torch.empty(T, H, device=dev)
+        ops.stream_step(xd, y=y.to(dev), carry=M.to(dev), write=b.to(dev), mult=0.5, y_bias=yb.to(dev), read=a.to(dev),
+                        norm_w=w.to(dev), eps=1e-5, out=out)
+        new = torch.einsum("st,jsh->jth", M.double(), xs.double()) + 0.5 * b.double()[None, :, None] * (y.double() + yb.double())[:, None, :]
+        u = torch.einsum("s,jsh->jh", a.double(), new)
+        worst = max(worst, _rel(xd, new), _rel(out, u / torch.sqrt((u * u).mean(-1, keepdim=True) + 1e-5) * w.double()))
+    return worst, 1e-5
+
+
+def check_decay_attention(dev) -> Tuple[float, float]:
+    """Linear attention with one decay per head over silu-activated q, k, v, two requests in a batch, then the norm over
+    all heads with a sigmoid gate."""
+    from .kernels import ops
+    heads, D, Dv, lens = 3, 24, 40, [21, 6]
+    kd, vd, T = heads * D, heads * Dv, sum(lens)
+    proj, decay, w = torch.randn(T, 2 * kd + 2 * vd), torch.tensor([0.5, 0.9, 0.99]), 1 + 0.3 * torch.randn(vd)
+    pd = proj.to(dev)
+    state = torch.zeros(2, heads, D, Dv, device=dev)
+    cu = torch.tensor([0, lens[0], T], dtype=torch.int32, device=dev)
+    slots = torch.tensor([1, 0], dtype=torch.int32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    o, act = torch.empty(T, vd, device=dev), torch.empty(T, vd, device=dev)
+    ops.decay_recurrent(pd[:, :kd], pd[:, kd:2 * kd], pd[:, 2 * kd:2 * kd + vd], decay.to(dev), True, state, cu, slots, 2, o, heads, D, Dv,
+                        1.0, err)
+    req = torch.cat([torch.zeros(lens[0]), torch.ones(lens[1])]).to(dev, torch.int32)
+    ops.rownorm_gate(o, pd[:, 2 * kd + vd:], w.to(dev), 1e-5, act, req, scale=1.2)
+    p64 = proj.double()
+    f = p64 / (1 + torch.exp(-p64))
+    want, at = torch.zeros(T, vd, dtype=torch.float64), 0
+    for n in lens:
+        S = torch.zeros(heads, D, Dv, dtype=torch.float64)
+        for t in range(at, at + n):
+            q, k, v = f[t, :kd].view(heads, D), f[t, kd:2 * kd].view(heads, D), f[t, 2 * kd:2 * kd + vd].view(heads, Dv)
+            S = decay.double()[:, None, None] * S + k[:, :, None] * v[:, None, :]
+            want[t] = torch.einsum("hdv,hd->hv", S, q).reshape(vd)
+        at += n
+    gated = 1.2 * want / torch.sqrt((want * want).mean(-1, keepdim=True) + 1e-5) * w.double() * torch.sigmoid(p64[:, 2 * kd + vd:])
+    return max(_rel(o, want), _rel(act, gated)), 2e-5
+
+
 CHECKS: List[Tuple[str, Callable]] = [
     ("embedding gather", check_embedding),
     ("rmsnorm + residual add", check_rmsnorm),
@@ -552,6 +599,8 @@ CHECKS: List[Tuple[str, Callable]] = [
     ("differential attention, float32 and mma.sync", check_diff_attention),
     ("attention without softmax, float32 and mma.sync", check_sigmoid_attention),
     ("product, tcgen05 with an activation in the epilogue", check_gemm_tc_activation),
+    ("residual of several streams: write, read and norm", check_streams),
+    ("decayed linear attention: recurrence, norm over all heads and gate", check_decay_attention),
     ("sampling", check_sampling),
     ("largest logits of a row", check_largest_logits),
 ]

@@ -316,6 +316,16 @@ def test_streams_in_one_pass(T, S, H, dtype):
     ops.stream_step(xs, y=dev(y)[:, :H], carry=dev(M), write=dev(b), mult=1.0, read=torch.ones(S, device="cuda"), out=total, req_of_token=req)
     last = P.plain_streams_write(new, y[:, :H].double(), M.double(), b.double(), 1.0)
     assert torch.allclose(total.cpu().double(), last.sum(0), atol=2e-5, rtol=1e-5)
+    # the same with everything on 16-byte boundaries (four columns a thread)
+    xs2, y2 = dev(xs0), dev(y[:, :H].contiguous())
+    ops.stream_step(xs2, y=y2, carry=dev(M), write=dev(b), mult=0.6, y_bias=dev(yb), read=dev(a), norm_w=dev(w), eps=1e-4, out=out,
+                    req_of_token=req)
+    assert torch.allclose(xs2.cpu().double().permute(1, 0, 2), P.plain_streams_write(sd, y[:, :H].double() + yb.double(), M.double(), b.double(), 0.6),
+                          atol=1e-5, rtol=1e-5)
+    ops.stream_step(xs2, y=y2, carry=dev(M), write=dev(b), mult=1.0, read=torch.ones(S, device="cuda"), out=total, req_of_token=req)
+    twice = P.plain_streams_write(P.plain_streams_write(sd, y[:, :H].double() + yb.double(), M.double(), b.double(), 0.6), y[:, :H].double(),
+                                  M.double(), b.double(), 1.0)
+    assert torch.allclose(total.cpu().double(), twice.sum(0), atol=5e-5, rtol=1e-5)
     # padding rows are left alone
     req[0] = -1
     before = xs.clone()
