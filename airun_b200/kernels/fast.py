@@ -68,7 +68,7 @@ DISABLED = set(filter(None, os.environ.get("AIRUN_DISABLE_FAST", "").split(","))
 def all_libraries():
     return [("gemm_tcgen05", None), ("gemm_tcgen05", {"AIRUN_FOLD_NORM": 1}), ("attention_plan", None), ("attention_mma", {"HD": 128}), ("attention_mma", {"HD": 64}),
             ("attention_tcgen05", {"HD": 128}), ("attention_tcgen05", {"HD": 64}), ("diff_attention_mma", None),
-            ("latent_attention_mma", None), ("sigmoid_attention_mma", None)]
+            ("latent_attention_mma", None), ("sigmoid_attention_mma", None), ("softmax_attention_mma", None)]
 
 
 def scratch_for(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:

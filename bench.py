@@ -1021,11 +1021,12 @@ def tagulix_pair(size: dict):
     layer runs.  Tagulix: four residual streams; a windowed softmax attention (window 1,024, half of each head rotated)
     and a pair of mixers side by side (causal softmax attention with a distance table, a sink and a query temperature,
     beside a decayed linear attention of half as many heads, 64 x 128) in turn; the third and fifth run use the first
-    layer's tensors and the sixth the second's; every layer routes a token to 4 of 16 + 2 experts (two groups of which
-    one is kept) of a quarter of the dense feed-forward size, without a gate: 2 W F multiply-adds where Qwen3 has 3."""
+    layer's tensors and the sixth the second's; every layer routes a token to 4 of 16 + 4 router outputs (four groups of
+    which two are kept; the last four return their input) with experts of a quarter of the dense feed-forward size,
+    without a gate: at most 2 W F multiply-adds where Qwen3 has 3."""
     from airun_b200.config import TagulixConfig
     W, F, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
-    moe = dict(kind="moe", expert=dict(ff=F // 4), router=dict(experts=16, top=4, identity=2, scale=2.0, groups=dict(count=2, keep=1)))
+    moe = dict(kind="moe", expert=dict(ff=F // 4), router=dict(experts=16, top=4, identity=4, scale=1.5, groups=dict(count=4, keep=2)))
     att = dict(type="attention", mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=0.1, mask=dict(size=1024),
                                             rot=dict(dims=64, base=10000.0)), mlp=moe)
     par = dict(type="parallel", mixer=dict(
@@ -1033,7 +1034,7 @@ def tagulix_pair(size: dict):
         right=dict(heads=H // 2, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(3 + i % 6) for i in range(H // 2)]),
         left_scale=1.0, right_scale=1.0), mlp=moe)
     layers = [att, par, dict(att, weights_of=0), par, dict(att, weights_of=0), dict(par, weights_of=1)]
-    tag = TagulixConfig.from_dict(dict(architecture="Tagulix", vocab=VEDIZEN_VOCAB, width=W, norm=dict(eps=1e-5), residual_mult=0.5,
+    tag = TagulixConfig.from_dict(dict(architecture="Tagulix", vocab=VEDIZEN_VOCAB, width=W, norm=dict(eps=1e-5), residual_mult=0.6,
                                        streams=4, layers=layers))
     return tag, vedizen_pair(size)[1]
 
@@ -1073,9 +1074,10 @@ def workload_tagulix(a) -> int:
                     "decayed linear attention: recurrence": (ops, "decay_recurrent", lambda t: 3 * t * (lin_in - Hl * 128 * 4.0 + lin_out),
                                                              lambda b: 3 * b * (Hl * 64 * 128 * 8.0), "hbm"),
                     "norm over all heads and gate": (ops, "rownorm_gate", lambda t: 3 * t * Hl * 128 * 10.0, lambda b: 3 * b * Hl * 128 * 10.0, "hbm"),
-                    "expert products (up + GELU, down)": (fast, "grouped_linear_bf16", lambda t: 6 * t * top * 4.0 * W * Fe,
+                    # a random router sends top * E / (E + 4) of a token's choices to experts with matrices
+                    "expert products (up + GELU, down)": (fast, "grouped_linear_bf16", lambda t: 6 * t * (top * E / (E + 4.0)) * 4.0 * W * Fe,
                                                           lambda b: 6 * min(E, b * top) * 2 * W * Fe * 2.0, "tensor"),
-                    "router with groups": (ops, "moe_route_grouped", lambda t: 6 * t * (E + 2 + 3 * top) * 4.0, lambda b: 6 * b * (E + 2 + 3 * top) * 4.0, "hbm"),
+                    "router with groups": (ops, "moe_route_grouped", lambda t: 6 * t * (E + 4 + 3 * top) * 4.0, lambda b: 6 * b * (E + 4 + 3 * top) * 4.0, "hbm"),
                     "rows to experts and back": (ops, "moe_scatter", lambda t: 6 * t * (W * 2 + top * W * 2.0), lambda b: 6 * b * (W * 2 + top * W * 2.0), "hbm"),
                     "sum of a token's experts": (ops, "moe_combine", lambda t: 6 * t * (top + 1) * W * 4.0, lambda b: 6 * b * (top + 1) * W * 4.0, "hbm"),
                 }
