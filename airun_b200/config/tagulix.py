@@ -233,7 +233,8 @@ class TagulixConfig(ModelConfig):
                             left_args=dict(num_heads=a["heads"], num_kv_heads=a["kv_heads"], key_dim=a["dim"], value_dim=a["vdim"],
                                            scale=a["scale"], norm_eps=self.norm_eps, qk_norm="weight",
                                            temp_coef=temp.get("coef", 0.0), temp_every=temp.get("every", 0),
-                                           distance_rows=a.get("distance_rows", DEFAULT_DISTANCE_ROWS),
+                                           # without a file to read the table's rows from: as many as bias_max allows
+                                           distance_rows=a.get("distance_rows", max(2, min(DEFAULT_DISTANCE_ROWS, 2 * (a["bias_max"] - 1)))),
                                            distance_far=a["bias_max"], sink=True),
                             right="decay_linear_attention",
                             right_args=dict(num_heads=r["heads"], key_dim=r["dim"], value_dim=r["vdim"], decay=r["decay"],
